@@ -37,7 +37,10 @@ def registered_architectures() -> list[str]:
 
 
 def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
-    archs = config_dict.get("architectures") or []
+    archs = list(config_dict.get("architectures") or [])
+    one = config_dict.get("architecture")             # some designs name a single one
+    if isinstance(one, str):
+        archs.append(one)
     for a in archs:
         if a in _ARCHITECTURES:
             return _ARCHITECTURES[a]

@@ -1,0 +1,280 @@
+// Routed feed-forward (mixture of experts) without a host round trip: every kernel reads the
+// routing from device memory, so a step can be captured in a CUDA graph.
+//
+//   moe_route_kernel    a warp a token: scores = softmax(router logits) in fp32 over all experts,
+//                       the `top` largest chosen (lowest index among equals), their scores kept as
+//                       weights (optionally renormalised over the chosen ones).
+//   moe_plan_kernel     one block: (token, choice) pairs counted per expert, the experts' ranges in
+//                       the sorted order, each pair's place, and the list of row tiles (expert,
+//                       first row) that the grouped products walk over.
+//   moe_gemm_kernel     grouped product over the sorted pairs, a block a (row tile, column tile):
+//                       FIRST: rows gathered from the tokens, W = the expert's row-interleaved
+//                       gate/up matrix, epilogue = clamped sigmoid-gated GLU; else rows = the first
+//                       product's output, W = the expert's down matrix, fp32 out.  The reduction
+//                       runs in a fixed order, so a pair's result does not depend on the batch.
+//   moe_combine_kernel  out[t] = sum over the token's choices, in the order chosen, of weight *
+//                       the pair's row.
+#include "common.cuh"
+
+namespace gf {
+
+constexpr int kMaxExperts = 256;
+constexpr int kRouteSlots = kMaxExperts / 32;
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int top,
+                                 int renorm, int* __restrict__ idx, float* __restrict__ wgt) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();
+  if (t >= T) return;
+  float s[kRouteSlots];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kRouteSlots; ++i) {
+    const int e = lane + 32 * i;
+    s[i] = e < E ? logits[(size_t)t * E + e] : -INFINITY;
+    mx = fmaxf(mx, s[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kRouteSlots; ++i) {
+    s[i] = lane + 32 * i < E ? expf(s[i] - mx) : -1.f;       // -1: no expert, or taken
+    sum += s[i] > 0.f ? s[i] : 0.f;
+  }
+  sum = warp_sum(sum);
+  float chosen_sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kRouteSlots; ++i)
+      if (s[i] > best) best = s[i], be = lane + 32 * i;       // ascending e: lowest index wins
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ob > best || (ob == best && oe < be)) best = ob, be = oe;
+    }
+#pragma unroll
+    for (int i = 0; i < kRouteSlots; ++i)
+      if (lane + 32 * i == be) s[i] = -1.f;
+    chosen_sum += best;
+    if (lane == 0) {
+      idx[(size_t)t * top + k] = be;
+      wgt[(size_t)t * top + k] = best / sum;
+    }
+  }
+  if (renorm) {
+    __syncwarp();
+    if (lane < top) wgt[(size_t)t * top + lane] *= sum / chosen_sum;
+  }
+}
+
+// Pairs p = t * top + k.  offsets[E + 1]; pos_of_pair[P]; pair_of_pos[P]; tiles: tile_expert[],
+// tile_row0[] (first sorted row of the tile), num_tiles[0].
+__global__ void moe_plan_kernel(const int* __restrict__ idx, int P, int E, int tile_rows,
+                                int* __restrict__ offsets, int* __restrict__ pos_of_pair,
+                                int* __restrict__ pair_of_pos, int* __restrict__ tile_expert,
+                                int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
+  __shared__ int count[kMaxExperts], start[kMaxExperts + 1];
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&count[idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = at;
+      offsets[e] = at;
+      for (int r = 0; r < count[e]; r += tile_rows) {
+        tile_expert[nt] = e;
+        tile_row0[nt] = at + r;
+        ++nt;
+      }
+      at += count[e];
+    }
+    start[E] = at;
+    offsets[E] = at;
+    num_tiles[0] = nt;
+  }
+  __syncthreads();
+  // places inside an expert's range in pair order (a pair's place is the number of earlier pairs
+  // of the same expert): deterministic, and a warp handles 32 pairs at a time per expert
+  for (int e = threadIdx.x >> 5; e < E; e += blockDim.x >> 5) {
+    const int lane = threadIdx.x & 31;
+    int at = start[e];
+    for (int p0 = 0; p0 < P; p0 += 32) {
+      const int p = p0 + lane;
+      const bool mine = p < P && idx[p] == e;
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int pos = at + __popc(m & ((1u << lane) - 1));
+        pos_of_pair[p] = pos;
+        pair_of_pos[pos] = p;
+      }
+      at += __popc(m);
+    }
+  }
+}
+
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float alpha,
+                                             float up_shift) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-alpha * g)) * (u + up_shift);
+}
+
+constexpr int kBM = 32, kBN = 64, kBK = 32;
+
+// FIRST: a [T, K] tokens (row of sorted place s = pair_of_pos[s] / top), w [E, 2F, K] (gate row,
+// up row, ...), out [P, F] of type T.  Else: a [P, K] (T), w [E, N, K], out [P, N] fp32.
+template <typename T, bool FIRST>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, int N, int K,
+                const int* __restrict__ offsets, const int* __restrict__ pair_of_pos, int top,
+                const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                const int* __restrict__ num_tiles, void* __restrict__ out_, float limit,
+                float alpha, float up_shift) {
+  __shared__ float As[kBM][kBK + 1], Ws[kBN][kBK + 1];
+  __shared__ int src_row[kBM];
+  pdl_trigger();
+  pdl_wait();
+  if ((int)blockIdx.x >= num_tiles[0]) return;
+  const int e = tile_expert[blockIdx.x], row0 = tile_row0[blockIdx.x];
+  const int rows = min(kBM, offsets[e + 1] - row0);
+  const int n0 = blockIdx.y * kBN;
+  const T* we = w + (size_t)e * N * K;
+  if (threadIdx.x < kBM) {
+    const int s = row0 + threadIdx.x;
+    src_row[threadIdx.x] = threadIdx.x < rows ? (FIRST ? pair_of_pos[s] / top : s) : -1;
+  }
+  __syncthreads();
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;    // rows 2 ty, 2 ty + 1; cols 4 tx ..
+  float acc[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += kBK) {
+    for (int i = threadIdx.x; i < kBM * kBK; i += 256) {
+      const int r = i / kBK, k = i - r * kBK;
+      const int sr = src_row[r];
+      As[r][k] = (sr >= 0 && k0 + k < K) ? to_f32(a[(size_t)sr * lda + k0 + k]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < kBN * kBK; i += 256) {
+      const int n = i / kBK, k = i - n * kBK;
+      Ws[n][k] = (n0 + n < N && k0 + k < K) ? to_f32(we[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kBK; ++k) {
+      const float a0 = As[2 * ty][k], a1 = As[2 * ty + 1][k];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float b = Ws[4 * tx + j][k];
+        acc[0][j] = fmaf(a0, b, acc[0][j]);
+        acc[1][j] = fmaf(a1, b, acc[1][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = 2 * ty + i;
+    if (r >= rows) continue;
+    const size_t s = (size_t)(row0 + r);
+    if (FIRST) {
+      T* out = (T*)out_;
+      const int F = N / 2;
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        const int n = n0 + 4 * tx + j;
+        if (n < N) {
+          // gate and up are rounded to the activation type as a plain product would store them
+          const float gt = to_f32(from_f32<T>(acc[i][j])), up = to_f32(from_f32<T>(acc[i][j + 1]));
+          out[s * F + n / 2] = from_f32<T>(clamped_glu(gt, up, limit, alpha, up_shift));
+        }
+      }
+    } else {
+      float* out = (float*)out_;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + 4 * tx + j;
+        if (n < N) out[s * N + n] = acc[i][j];
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
+                                   const float* __restrict__ wgt, int top, int N,
+                                   T* __restrict__ out) {
+  const int t = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k)
+      acc = fmaf(wgt[(size_t)t * top + k], y[(size_t)pos_of_pair[(size_t)t * top + k] * N + n], acc);
+    out[(size_t)t * N + n] = from_f32<T>(acc);
+  }
+}
+
+}  // namespace gf
+
+using namespace gf;
+using bf = __nv_bfloat16;
+
+GF_DEFINE_PDL_SWITCH
+
+GF_EXPORT int gf_moe_tile_rows() { return kBM; }
+
+GF_EXPORT int gf_moe_route(const float* logits, int T, int E, int top, int renorm, int* idx,
+                           float* wgt, void* stream) {
+  if (T <= 0) return 0;
+  if (E > kMaxExperts || top > E || top > 32) return -3;
+  return launch_kernel(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream,
+                       logits, T, E, top, renorm, idx, wgt);
+}
+
+GF_EXPORT int gf_moe_plan(const int* idx, int P, int E, int* offsets, int* pos_of_pair,
+                          int* pair_of_pos, int* tile_expert, int* tile_row0, int* num_tiles,
+                          void* stream) {
+  if (P <= 0) return 0;
+  if (E > kMaxExperts) return -3;
+  return launch_kernel(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, idx, P, E,
+                       kBM, offsets, pos_of_pair, pair_of_pos, tile_expert, tile_row0, num_tiles);
+}
+
+// first != 0: gate/up product with the activation; out [P, N / 2] (dtype).  Else down: out fp32.
+GF_EXPORT int gf_moe_gemm(const void* a, int lda, const void* w, int N, int K, const int* offsets,
+                          const int* pair_of_pos, int top, const int* tile_expert,
+                          const int* tile_row0, const int* num_tiles, int max_tiles, void* out,
+                          int first, float limit, float alpha, float up_shift, int dtype,
+                          void* stream) {
+  if (max_tiles <= 0) return 0;
+  auto st = (cudaStream_t)stream;
+  const dim3 grid(max_tiles, (N + kBN - 1) / kBN), block(256);
+#define GF_GO(T, FIRST)                                                                          \
+  return launch_kernel(moe_gemm_kernel<T, FIRST>, grid, block, 0, st, (const T*)a, lda,          \
+                       (const T*)w, N, K, offsets, pair_of_pos, top, tile_expert, tile_row0,      \
+                       num_tiles, out, limit, alpha, up_shift)
+  if (dtype == GF_F32) {
+    if (first) GF_GO(float, true);
+    GF_GO(float, false);
+  }
+  if (first) GF_GO(bf, true);
+  GF_GO(bf, false);
+#undef GF_GO
+}
+
+GF_EXPORT int gf_moe_combine(const float* y, const int* pos_of_pair, const float* wgt, int T,
+                             int top, int N, void* out, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  auto st = (cudaStream_t)stream;
+  if (dtype == GF_F32)
+    return launch_kernel(moe_combine_kernel<float>, dim3(T), dim3(256), 0, st, y, pos_of_pair, wgt,
+                         top, N, (float*)out);
+  return launch_kernel(moe_combine_kernel<bf>, dim3(T), dim3(256), 0, st, y, pos_of_pair, wgt, top,
+                       N, (bf*)out);
+}

@@ -1,0 +1,129 @@
+// Kernels on a 32-bit residual stream whose norms sit on the sublayers' OUTPUTS:
+//   * embedding gather with a scale, written as the fp32 stream and (bf16 path) its rounding,
+//   * x' = x + rmsnorm(y) * gamma: the norm of a sublayer's output added to the stream, with the
+//     activation-type copy of x' that the next sublayer's products read,
+//   * the clamped, sigmoid-gated GLU activation over row-interleaved gate/up values.
+// Arithmetic is fp32; T is the activation type (float for the 32-bit path, bf16 for serving).
+#include "common.cuh"
+
+namespace gf {
+
+// out[t, :] = float(W[ids[t], :]) * scale; act[t, :] = T(out[t, :]) when asked for.
+template <typename W, typename T>
+__global__ void embedding_scaled_kernel(const int* __restrict__ ids, const W* __restrict__ w,
+                                        float scale, float* __restrict__ out, T* __restrict__ act,
+                                        int H) {
+  const int t = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  const W* src = w + (size_t)ids[t] * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float v = to_f32(src[j]) * scale;
+    out[(size_t)t * H + j] = v;
+    if (act) act[(size_t)t * H + j] = from_f32<T>(v);
+  }
+}
+
+// One block per row.  y: the sublayer's output (Y = float or T).  out = x + y * gamma / rms(y) with
+// rms = sqrtf(mean(y^2) + eps); act (nullable) = T(out).  out may alias x.
+template <typename Y, typename T>
+__global__ void outnorm_add_kernel(const float* __restrict__ x, const Y* __restrict__ y,
+                                   const float* __restrict__ gamma, float eps,
+                                   float* __restrict__ out, T* __restrict__ act, int H) {
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  const size_t base = (size_t)r * H;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float v = to_f32(y[base + j]);
+    row[j] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float v = x[base + j] + row[j] * gamma[j] / rms;
+    out[base + j] = v;
+    if (act) act[base + j] = from_f32<T>(v);
+  }
+}
+
+// gu[t, 2 i] = gate, gu[t, 2 i + 1] = up.  g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + up_shift).
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float alpha,
+                                             float up_shift) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-alpha * g)) * (u + up_shift);
+}
+
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t total,
+                                   float limit, float alpha, float up_shift) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(clamped_glu(to_f32(gu[2 * i]), to_f32(gu[2 * i + 1]), limit, alpha,
+                                     up_shift));
+}
+
+}  // namespace gf
+
+using namespace gf;
+using bf = __nv_bfloat16;
+
+GF_DEFINE_PDL_SWITCH
+
+GF_EXPORT int gf_embedding_scaled(const int* ids, const void* w, int w_dtype, float scale,
+                                  float* out, void* act, int act_dtype, int T, int H,
+                                  void* stream) {
+  if (T <= 0) return 0;
+  auto st = (cudaStream_t)stream;
+  const dim3 grid(T), block(H >= 1024 ? 256 : 128);
+  if (w_dtype == GF_F32) {
+    if (act && act_dtype != GF_F32) return -2;
+    return launch_kernel(embedding_scaled_kernel<float, float>, grid, block, 0, st, ids,
+                         (const float*)w, scale, out, (float*)act, H);
+  }
+  if (act && act_dtype != GF_BF16) return -2;
+  return launch_kernel(embedding_scaled_kernel<bf, bf>, grid, block, 0, st, ids, (const bf*)w,
+                       scale, out, (bf*)act, H);
+}
+
+GF_EXPORT int gf_outnorm_add(const float* x, const void* y, int y_dtype, const float* gamma,
+                             float eps, float* out, void* act, int act_dtype, int R, int H,
+                             void* stream) {
+  if (R <= 0) return 0;
+  auto st = (cudaStream_t)stream;
+  const dim3 grid(R), block(H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 48 * 1024) return -4;
+  if (act_dtype == GF_F32) {
+    if (y_dtype != GF_F32) return -2;
+    return launch_kernel(outnorm_add_kernel<float, float>, grid, block, smem, st, x,
+                         (const float*)y, gamma, eps, out, (float*)act, H);
+  }
+  if (y_dtype == GF_F32)
+    return launch_kernel(outnorm_add_kernel<float, bf>, grid, block, smem, st, x, (const float*)y,
+                         gamma, eps, out, (bf*)act, H);
+  return launch_kernel(outnorm_add_kernel<bf, bf>, grid, block, smem, st, x, (const bf*)y, gamma,
+                       eps, out, (bf*)act, H);
+}
+
+GF_EXPORT int gf_clamped_glu(const void* gu, void* out, int T, int I, float limit, float alpha,
+                             float up_shift, int dtype, void* stream) {
+  const size_t total = (size_t)T * I;
+  if (total == 0) return 0;
+  auto st = (cudaStream_t)stream;
+  const size_t want = (total + 255) / 256;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  if (dtype == GF_F32)
+    return launch_kernel(clamped_glu_kernel<float>, dim3(blocks), dim3(256), 0, st,
+                         (const float*)gu, (float*)out, total, limit, alpha, up_shift);
+  return launch_kernel(clamped_glu_kernel<bf>, dim3(blocks), dim3(256), 0, st, (const bf*)gu,
+                       (bf*)out, total, limit, alpha, up_shift);
+}

@@ -93,6 +93,61 @@ def embedding(token_ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def embedding_scaled(token_ids: torch.Tensor, weight: torch.Tensor, scale: float,
+                     want_act: bool):
+    """``x = float(W[ids]) * scale`` as the fp32 residual stream; with ``want_act`` also its
+    rounding to the weight's dtype (what the first sublayer's products read), else ``None``."""
+    _cuda(token_ids, weight)
+    assert token_ids.dtype == torch.int32 and token_ids.is_contiguous() and weight.is_contiguous()
+    T, (V, H) = token_ids.numel(), weight.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=weight.device)
+    act = torch.empty((T, H), dtype=weight.dtype, device=weight.device) if want_act else None
+    f = _fn("stream_ops", "gf_embedding_scaled",
+            [c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_void_p])
+    _ok(f(_p(token_ids), _p(weight), _code(weight.dtype), float(scale), _p(out), _p(act),
+          _code(weight.dtype), T, H, _stream()), "embedding_scaled")
+    return out, act
+
+
+def outnorm_add(x: torch.Tensor, y: torch.Tensor, gamma: torch.Tensor, eps: float,
+                act_dtype: torch.dtype, want_act: bool = True):
+    """``x' = x + y * gamma / rms(y)`` (fp32; ``x`` the fp32 stream, ``y`` a sublayer's output in
+    fp32 or the activation dtype, ``gamma`` fp32) and, with ``want_act``, ``x'`` rounded to
+    ``act_dtype`` for the next sublayer's products."""
+    _cuda(x, y, gamma)
+    assert x.dtype == torch.float32 and gamma.dtype == torch.float32
+    assert x.dim() == 2 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape
+    R, H = x.shape
+    out = torch.empty_like(x)
+    act = torch.empty((R, H), dtype=act_dtype, device=x.device) \
+        if want_act and act_dtype != torch.float32 else None
+    f = _fn("stream_ops", "gf_outnorm_add",
+            [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_void_p])
+    rc = f(_p(x), _p(y), _code(y.dtype), _p(gamma), float(eps), _p(out), _p(act),
+           _code(act_dtype), R, H, _stream())
+    if rc == -4:
+        raise ValueError(f"rows of {H} channels do not fit the norm kernel's shared memory")
+    _ok(rc, "outnorm_add")
+    return out, (out if act_dtype == torch.float32 else act)
+
+
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float, up_shift: float
+                ) -> torch.Tensor:
+    """``gate_up [T, 2 I]`` with gate and up interleaved -> ``min(g, limit) * sigmoid(alpha *
+    min(g, limit)) * (clamp(u, -limit, limit) + up_shift)``, ``[T, I]``."""
+    _cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
+    T, I = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn("stream_ops", "gf_clamped_glu",
+            [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p])
+    _ok(f(_p(gate_up), _p(out), T, I, float(limit), float(alpha), float(up_shift),
+          _code(gate_up.dtype), _stream()), "clamped_glu")
+    return out
+
+
 # ----------------------------------------------------------------------------- add + rmsnorm
 def add_rmsnorm(x: torch.Tensor, delta, gamma: torch.Tensor, eps: float, rows=None,
                 want_sum: bool = True, out_dtype=None):
@@ -268,6 +323,16 @@ def qkv_rope_write(x, linear, table, rot, positions, slot_mapping, pages, nh, nk
     from . import gemm_prefill
     return gemm_prefill.qkv_rope_write(x, linear.weight, linear._bias_f32, table, rot, positions,
                                        slot_mapping, pages, nh, nkv, hd)
+
+
+def bmm_f32_out(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Batched product ``[B, M, K] @ [B, K, N]`` with an fp32 result (fp32 accumulation; from
+    fp32 operands a true 32-bit product: the reduced-precision matrix modes stay off)."""
+    _cuda(a, b)
+    if a.dtype == torch.float32:
+        assert not torch.backends.cuda.matmul.allow_tf32
+        return torch.bmm(a, b)
+    return torch.bmm(a, b, out_dtype=torch.float32)
 
 
 from .linear import GatedLinear, Linear, add_to  # noqa: E402,F401

@@ -1,0 +1,57 @@
+"""Latent attention over a paged cache of one latent vector and one rotated key part a token
+(``csrc/latent_attention.cu``)."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import _code, _cuda, _fn, _ok, _p, _stream
+
+
+def prepare(qd: torch.Tensor, H: int, D: int, R: int, C: int, rot: int, freq: torch.Tensor,
+            cnorm_w: torch.Tensor, eps: float, positions: torch.Tensor, slot_mapping,
+            c_pages: torch.Tensor, r_pages: torch.Tensor) -> torch.Tensor:
+    """``qd [T, H (D + R) + C + R]``: the heads' queries ``[D plain | R rotated]``, then the
+    down-projection ``[C | R]``.  Writes the normed latent vector and the rotated key part into the
+    token's cache slot (``slot_mapping``; ``None``: no write) and returns the heads' rotated query
+    parts ``[T, H, R]`` in fp32."""
+    _cuda(qd, freq, cnorm_w, positions, slot_mapping, c_pages, r_pages)
+    T = qd.shape[0]
+    assert qd.dim() == 2 and qd.stride(1) == 1 and qd.shape[1] == H * (D + R) + C + R
+    assert freq.dtype == torch.float32 and freq.numel() == rot // 2
+    assert cnorm_w.dtype == torch.float32 and cnorm_w.numel() == C
+    assert c_pages.is_contiguous() and r_pages.is_contiguous() and c_pages.dtype == qd.dtype
+    assert c_pages.shape[-1] == C and r_pages.shape[-1] == R
+    q_rot = torch.empty((T, H, R), dtype=torch.float32, device=qd.device)
+    f = _fn("latent_attention", "gf_latent_prepare",
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _ok(f(_p(qd), qd.stride(0), H, D, R, C, rot, _p(freq), _p(cnorm_w), float(eps),
+          _p(positions), _p(slot_mapping), _p(c_pages), _p(r_pages), _p(q_rot), T,
+          _code(qd.dtype), _stream()), "latent_prepare")
+    return q_rot
+
+
+def attention(q_lat: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor,
+              r_pages: torch.Tensor, block_table: torch.Tensor, ctx, window: int, scale: float,
+              page_size: int) -> torch.Tensor:
+    """``q_lat [H, T, C]`` and ``q_rot [T, H, R]`` in fp32 against the cache; returns the
+    softmax-weighted latent vectors ``[H, T, C]`` in the cache's dtype."""
+    _cuda(q_lat, q_rot, c_pages, r_pages, block_table)
+    H, T, C = q_lat.shape
+    R = q_rot.shape[2]
+    assert q_lat.dtype == torch.float32 and q_lat.is_contiguous()
+    assert q_rot.dtype == torch.float32 and q_rot.is_contiguous() and q_rot.shape[:2] == (T, H)
+    out = torch.empty((H, T, C), dtype=c_pages.dtype, device=q_lat.device)
+    f = _fn("latent_attention", "gf_latent_attention",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    rc = f(_p(q_lat), _p(q_rot), _p(c_pages), _p(r_pages), _p(block_table),
+           block_table.stride(0), _p(ctx.seq_of_token), _p(ctx.positions), _p(out), T, H, C, R,
+           int(page_size), int(window), float(scale), _code(c_pages.dtype), _stream())
+    if rc == -3:
+        raise ValueError(f"latent attention takes latent vectors of up to 512 channels whose key "
+                         f"tile fits shared memory; got kv_rank={C}, rot_dim={R}")
+    _ok(rc, "latent_attention")
+    return out

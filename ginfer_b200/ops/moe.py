@@ -1,0 +1,108 @@
+"""Routed feed-forward: routing, the plan of a step's (token, expert) pairs and the grouped
+products, all on the device (``csrc/moe.cu``)."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import _code, _cuda, _fn, _ok, _p, _stream, load_library
+
+_tile_rows = None
+
+
+def tile_rows() -> int:
+    global _tile_rows
+    if _tile_rows is None:
+        _tile_rows = int(load_library("moe").gf_moe_tile_rows())
+    return _tile_rows
+
+
+def route(logits: torch.Tensor, top: int, renormalize: bool):
+    """fp32 ``logits [T, E]`` -> ``(experts [T, top] int32, weights [T, top] fp32)``: softmax over
+    all experts, the ``top`` largest, lowest index among equals."""
+    _cuda(logits)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
+    T, E = logits.shape
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    wgt = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    f = _fn("moe", "gf_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                    c_void_p])
+    rc = f(_p(logits), T, E, int(top), int(bool(renormalize)), _p(idx), _p(wgt), _stream())
+    if rc == -3:
+        raise ValueError(f"the router kernel takes up to 256 experts and 32 choices, got {E}, {top}")
+    _ok(rc, "moe_route")
+    return idx, wgt
+
+
+class Plan:
+    """Where every (token, choice) pair sits once the pairs are sorted by expert."""
+
+    def __init__(self, idx: torch.Tensor, num_experts: int):
+        T, top = idx.shape
+        P = T * top
+        dev = idx.device
+        self.pairs, self.top, self.num_experts = P, top, num_experts
+        self.max_tiles = -(-P // tile_rows()) + num_experts
+        ints = torch.empty(num_experts + 1 + 2 * P + 2 * self.max_tiles + 1, dtype=torch.int32,
+                           device=dev)
+        at = 0
+
+        def take(n):
+            nonlocal at
+            t = ints[at:at + n]
+            at += n
+            return t
+        self.offsets, self.pos_of_pair, self.pair_of_pos = take(num_experts + 1), take(P), take(P)
+        self.tile_expert, self.tile_row0 = take(self.max_tiles), take(self.max_tiles)
+        self.num_tiles = take(1)
+        f = _fn("moe", "gf_moe_plan", [c_void_p, c_int, c_int] + [c_void_p] * 7)
+        rc = f(_p(idx), P, num_experts, _p(self.offsets), _p(self.pos_of_pair),
+               _p(self.pair_of_pos), _p(self.tile_expert), _p(self.tile_row0), _p(self.num_tiles),
+               _stream())
+        _ok(rc, "moe_plan")
+
+
+def grouped_glu(x: torch.Tensor, w_gate_up: torch.Tensor, plan: Plan, limit: float, alpha: float,
+                up_shift: float) -> torch.Tensor:
+    """``x [T, K]``, ``w_gate_up [E, 2 F, K]`` (gate row, up row, ...) -> the activated gate/up
+    product of every pair, in sorted order: ``[P, F]``."""
+    _cuda(x, w_gate_up)
+    E, N, K = w_gate_up.shape
+    assert x.dtype == w_gate_up.dtype and x.stride(1) == 1 and x.shape[1] == K
+    assert w_gate_up.is_contiguous()
+    out = torch.empty((plan.pairs, N // 2), dtype=x.dtype, device=x.device)
+    _gemm(x, w_gate_up, plan, out, True, limit, alpha, up_shift)
+    return out
+
+
+def grouped_down(y: torch.Tensor, w_down: torch.Tensor, plan: Plan) -> torch.Tensor:
+    """``y [P, F]`` (sorted pairs), ``w_down [E, N, F]`` -> ``[P, N]`` fp32."""
+    _cuda(y, w_down)
+    E, N, K = w_down.shape
+    assert y.dtype == w_down.dtype and y.is_contiguous() and y.shape == (plan.pairs, K)
+    out = torch.empty((plan.pairs, N), dtype=torch.float32, device=y.device)
+    _gemm(y, w_down, plan, out, False, 0.0, 0.0, 0.0)
+    return out
+
+
+def _gemm(a, w, plan, out, first, limit, alpha, up_shift):
+    f = _fn("moe", "gf_moe_gemm",
+            [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+             c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float, c_int,
+             c_void_p])
+    _ok(f(_p(a), a.stride(0), _p(w), w.shape[1], w.shape[2], _p(plan.offsets),
+          _p(plan.pair_of_pos), plan.top, _p(plan.tile_expert), _p(plan.tile_row0),
+          _p(plan.num_tiles), plan.max_tiles, _p(out), int(first), float(limit), float(alpha),
+          float(up_shift), _code(a.dtype), _stream()), "moe_gemm")
+
+
+def combine(y: torch.Tensor, plan: Plan, weights: torch.Tensor, num_tokens: int) -> torch.Tensor:
+    """``out[t] = sum_k weights[t, k] * y[place of pair (t, k)]``, fp32."""
+    N = y.shape[1]
+    out = torch.empty((num_tokens, N), dtype=torch.float32, device=y.device)
+    f = _fn("moe", "gf_moe_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                      c_int, c_void_p])
+    _ok(f(_p(y), _p(plan.pos_of_pair), _p(weights), num_tokens, plan.top, N, _p(out), 0,
+          _stream()), "moe_combine")
+    return out

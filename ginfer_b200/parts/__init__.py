@@ -5,5 +5,6 @@ from .base import (Block, Embedding, FeedForward, Head, LazyNorm, Mixer, Norm, P
                    make_part, register_block, register_feed_forward, register_mixer,
                    register_norm, register_part, register_position)
 from .plan import LayerSpec, ModelPlan, PartSpec, RunEntry, sequential_run
-from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401  (register)
+from . import (attention, block, delta_rule, embedding, feed_forward, latent_attention, norm,  # noqa: F401
+               position, routed)
 from .model import DecoderModel

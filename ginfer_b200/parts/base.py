@@ -26,7 +26,12 @@ class TensorSpec:
       drawn N(0, 0.02).
     * ``bias``: kept in the compute dtype unless stored in 32-bit, which stays; N(0, 0.02).
     * ``norm``: like ``bias`` but drawn 1 + N(0, 0.02).
+    * ``f32``: a small tensor that enters 32-bit arithmetic (a router, decay constants, norm
+      weights stored around zero); always kept in 32-bit; N(0, 0.02).
     * ``int``: integer table, kept as int32; drawn uniform in ``[0, int_high)``.
+
+    A size of ``-1`` in ``shape`` stands for "whatever the file has" (a rank that only the
+    tensor's own shape gives); random weights cannot be drawn for such a tensor.
     """
     name: str
     shape: tuple[int, ...]

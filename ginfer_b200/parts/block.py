@@ -95,3 +95,55 @@ class PreNormBlock(Block):
 
 
 register_block("prenorm", PreNormBlock)
+
+
+class OutputNormBlock(Block):
+    """Norms on the sublayers' outputs: ``x <- x + norm1(mixer(x))``, then
+    ``x <- x + norm2(ff(x))``; the sublayers read the stream itself.  The stream ``x`` is fp32;
+    the kernel that adds a normed output to it also writes the sum rounded to the activation
+    dtype, which is what the next sublayer's products read (it travels to the next block in
+    ``ctx.extras["act_copy"]``; a block that does not find its own ``x`` there rounds it anew).
+    A feed-forward that routes in 32-bit finds the stream in ``ctx.extras["stream"]``.  A layer
+    without a feed-forward is the first line alone."""
+
+    def __init__(self, layer_spec):
+        self.spec = layer_spec
+        self.mixer = make_part("mixer", layer_spec.mixer)
+        self.mixer_norm = make_part("norm", layer_spec.mixer_norm)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = make_part("feed_forward", layer_spec.feed_forward)
+            self.feed_forward_norm = make_part("norm", layer_spec.feed_forward_norm)
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm,
+                                 self.feed_forward) if p is not None)
+
+    def tensor_specs(self):
+        out = []
+        for p in self.parts():
+            out.extend(p.tensor_specs())
+        return out
+
+    def load(self, tensors, dtype, device):
+        for p in self.parts():
+            p.load(tensors, dtype, device)
+
+    def forward(self, x, delta, ctx, cache):
+        if delta is not None:
+            x = x.float() + delta.float()
+        elif x.dtype != torch.float32:
+            x = x.float()
+        kept = ctx.extras.get("act_copy")
+        h = kept[1] if kept is not None and kept[0] is x else x.to(ctx.dtype)
+        a = self.mixer.forward(h, ctx, cache)
+        x, h = self.mixer_norm.add_output(x, a, ctx.dtype)
+        if self.feed_forward is not None:
+            ctx.extras["stream"] = x
+            m = self.feed_forward.forward(h, ctx)
+            x, h = self.feed_forward_norm.add_output(x, m, ctx.dtype)
+        ctx.extras["act_copy"] = (x, h)
+        return x, None
+
+
+register_block("outnorm", OutputNormBlock)

@@ -14,8 +14,13 @@ from .base import Embedding, Head, TensorSpec, register_part
 
 
 class TokenEmbedding(Embedding):
-    def __init__(self, vocab_size: int, hidden_size: int, name: str = "model.embed_tokens.weight"):
+    """``scale``: the rows are multiplied by it and leave as the fp32 residual stream (their
+    rounding to the activation dtype is left in ``ctx.extras["act_copy"]`` for the first block)."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, name: str = "model.embed_tokens.weight",
+                 scale: float | None = None):
         self.vocab_size, self.hidden_size, self.name = int(vocab_size), int(hidden_size), name
+        self.scale = None if scale is None else float(scale)
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self):
@@ -25,7 +30,12 @@ class TokenEmbedding(Embedding):
         self.weight = tensors[self.name]
 
     def forward(self, token_ids, ctx):
-        return ops.embedding(token_ids, self.weight)
+        if self.scale is None:
+            return ops.embedding(token_ids, self.weight)
+        x, act = ops.embedding_scaled(token_ids, self.weight, self.scale,
+                                      want_act=self.weight.dtype != torch.float32)
+        ctx.extras["act_copy"] = (x, x if act is None else act)
+        return x
 
 
 class LinearHead(Head):

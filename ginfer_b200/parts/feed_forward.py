@@ -7,6 +7,8 @@ joined at load into one matrix so that one product reads ``y`` once.
 """
 from __future__ import annotations
 
+import torch
+
 from .. import ops
 from .base import FeedForward, Summed, TensorSpec, register_feed_forward
 
@@ -47,3 +49,35 @@ class SwiGLU(FeedForward):
 
 
 register_feed_forward("swiglu", SwiGLU)
+
+
+class ClampedGLU(FeedForward):
+    """``g = min(x W_g^T, limit)``, ``u = clamp(x W_u^T, -limit, limit)``,
+    ``z = g * sigmoid(alpha g) * (u + up_shift)``, ``m = z W_d^T``; no biases.  The defaults
+    (``alpha`` 1.702: the sigmoid form of GELU; ``up_shift`` 1) are those of the designs that use
+    it so far.  The output leaves in fp32 for the norm that follows it."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float,
+                 alpha: float = 1.702, up_shift: float = 1.0, prefix: str = "mlp",
+                 gate_name: str = "gate", up_name: str = "up", down_name: str = "down"):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit, self.alpha, self.up_shift = float(limit), float(alpha), float(up_shift)
+        p = prefix + "." if prefix else ""
+        self.gate_key, self.up_key, self.down_key = p + gate_name, p + up_name, p + down_name
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return [TensorSpec(self.gate_key, (i, h)), TensorSpec(self.up_key, (i, h)),
+                TensorSpec(self.down_key, (h, i))]
+
+    def load(self, tensors, dtype, device):
+        g, u = tensors[self.gate_key], tensors[self.up_key]
+        self.gate_up = ops.Linear(torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]))
+        self.down = ops.Linear(tensors[self.down_key], None, out_dtype=torch.float32)
+
+    def forward(self, x, ctx):
+        z = ops.clamped_glu(self.gate_up(x), self.limit, self.alpha, self.up_shift)
+        return self.down(z)
+
+
+register_feed_forward("clamped_glu", ClampedGLU)

@@ -87,5 +87,6 @@ class DecoderModel:
             _, n = self.final_norm.forward(x.tensor, None, rows=ctx.logit_rows, want_sum=False,
                                            out_dtype=ctx.dtype)
         else:
-            _, n = self.final_norm.forward(x, delta, rows=ctx.logit_rows, want_sum=False)
+            _, n = self.final_norm.forward(x, delta, rows=ctx.logit_rows, want_sum=False,
+                                           out_dtype=ctx.dtype)
         return self.head.forward(n, ctx)

@@ -15,17 +15,31 @@ from .base import LazyNorm, Norm, TensorSpec, register_norm
 
 
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float, weight_name: str = "weight"):
+    """``weight_offset``: the stored weight is an offset from this value (1.0 for weights stored
+    around zero: the norm multiplies by ``1 + w``); the sum is formed once, in 32-bit, at load."""
+
+    def __init__(self, size: int, eps: float, weight_name: str = "weight",
+                 weight_offset: float = 0.0):
         self.size = int(size)
         self.eps = float(eps)
         self.weight_name = weight_name
+        self.weight_offset = float(weight_offset)
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.weight_name, (self.size,), "norm")]
+        return [TensorSpec(self.weight_name, (self.size,),
+                           "f32" if self.weight_offset else "norm")]
 
     def load(self, tensors, dtype, device):
         self.weight = tensors[self.weight_name]
+        if self.weight_offset:
+            self.weight = (self.weight.float() + self.weight_offset).contiguous()
+
+    def add_output(self, x, y, act_dtype, want_act=True):
+        """For blocks whose norms sit on the sublayers' outputs: ``x' = x + norm(y)`` on the fp32
+        stream ``x``; returns ``(x', x' in act_dtype or None)``."""
+        w = self.weight if self.weight.dtype == torch.float32 else self.weight.float()
+        return ops.outnorm_add(x, y, w, self.eps, act_dtype, want_act)
 
     def forward(self, x, delta=None, rows=None, want_sum=True, out_dtype=None):
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, rows=rows, want_sum=want_sum,
@@ -35,7 +49,7 @@ class RMSNorm(Norm):
         return LazyNorm(summed, self.weight, self.eps, dtype)
 
     def fold_weight(self):
-        return self.weight
+        return self.weight if not self.weight_offset else None
 
 
 register_norm("rmsnorm", RMSNorm)

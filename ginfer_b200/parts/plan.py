@@ -23,12 +23,13 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: an arrangement (``block``) of a mixer, a feed-forward and their norms.
-    ``prefix`` is the tensor-name prefix of the layer (``model.layers.3``)."""
+    ``prefix`` is the tensor-name prefix of the layer (``model.layers.3``).  A layer without a
+    feed-forward has ``None`` for it and its norm (blocks that allow it say so)."""
     prefix: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: PartSpec | None
     block: PartSpec = PartSpec("prenorm")
 
 

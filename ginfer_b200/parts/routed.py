@@ -1,0 +1,63 @@
+"""Routed feed-forward (mixture of experts).
+
+Router logits ``z = h W_r^T`` in 32-bit from the fp32 stream, scores ``softmax(z)`` over ALL
+experts, the ``top_k`` largest chosen; a token's output is the sum of the chosen experts' outputs
+weighted by their scores (as they are, or renormalised over the chosen ones with
+``renormalize``).  An expert is a clamped GLU (see :class:`ClampedGLU`) without biases, stored as
+``<prefix>.e<i>.gate|up|down``.
+
+Nothing returns to the host inside a step: the pairs (token, expert) are sorted by expert on the
+device and two grouped products walk over them.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import moe
+from .base import FeedForward, TensorSpec, register_feed_forward
+
+
+class RoutedGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, num_experts: int,
+                 top_k: int, renormalize: bool = False, alpha: float = 1.702,
+                 up_shift: float = 1.0, prefix: str = "mlp"):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.E, self.top = int(num_experts), int(top_k)
+        if not (0 < self.top <= self.E):
+            raise ValueError(f"{self.top} of {self.E} experts cannot be chosen")
+        self.limit, self.alpha, self.up_shift = float(limit), float(alpha), float(up_shift)
+        self.renormalize = bool(renormalize)
+        self.prefix = prefix + "." if prefix else ""
+
+    def tensor_specs(self):
+        h, f = self.hidden_size, self.intermediate_size
+        out = []
+        for e in range(self.E):
+            p = f"{self.prefix}e{e}."
+            out += [TensorSpec(p + "gate", (f, h)), TensorSpec(p + "up", (f, h)),
+                    TensorSpec(p + "down", (h, f))]
+        out.append(TensorSpec(self.prefix + "router", (self.E, h), "f32"))
+        return out
+
+    def load(self, tensors, dtype, device):
+        f, h = self.intermediate_size, self.hidden_size
+        gu = [torch.stack([tensors[f"{self.prefix}e{e}.gate"], tensors[f"{self.prefix}e{e}.up"]],
+                          dim=1).reshape(2 * f, h) for e in range(self.E)]
+        self.w_gate_up = torch.stack(gu).contiguous()                       # [E, 2 F, H]
+        self.w_down = torch.stack([tensors[f"{self.prefix}e{e}.down"]
+                                   for e in range(self.E)]).contiguous()    # [E, H, F]
+        self.router = ops.Linear(tensors[self.prefix + "router"].float())
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        stream = ctx.extras.get("stream")
+        h32 = stream if (stream is not None and stream.shape == x.shape
+                         and stream.dtype == torch.float32) else x.float()
+        idx, wgt = moe.route(self.router(h32), self.top, self.renormalize)
+        plan = moe.Plan(idx, self.E)
+        y = moe.grouped_glu(x, self.w_gate_up, plan, self.limit, self.alpha, self.up_shift)
+        return moe.combine(moe.grouped_down(y, self.w_down, plan), plan, wgt, T)
+
+
+register_feed_forward("routed_glu", RoutedGLU)

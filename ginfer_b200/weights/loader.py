@@ -50,6 +50,8 @@ def kept_dtype(role: str, stored: torch.dtype, compute: torch.dtype) -> torch.dt
     """The dtype a tensor of ``role`` stored as ``stored`` has in memory."""
     if role == "int":
         return torch.int32
+    if role == "f32":
+        return torch.float32
     if compute == torch.float32:
         return torch.float32
     if role in ("bias", "norm") and stored in (torch.float32, torch.float64):
@@ -70,7 +72,8 @@ def check_and_convert(specs, available: dict, fetch, model_dir: str, compute: to
     for n, s in wanted.items():
         if n in available:
             shape, dt = available[n]
-            if tuple(shape) != tuple(s.shape):
+            if len(shape) != len(s.shape) or any(w >= 0 and g != w
+                                                   for g, w in zip(shape, s.shape)):
                 wrong_shape.append((n, tuple(shape), tuple(s.shape)))
             if (s.role == "int") != (dt in _INTS) or (dt not in _FLOATS and dt not in _INTS):
                 wrong_dtype.append((n, dt, s.role))

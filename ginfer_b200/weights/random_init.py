@@ -26,6 +26,9 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 def draw_tensor(spec, seed: int, std: float = 0.02, device="cpu") -> torch.Tensor:
     """One tensor of a :class:`~ginfer_b200.parts.base.TensorSpec`, fp32 (int32 for tables)."""
+    if any(n < 0 for n in spec.shape):
+        raise ValueError(f"tensor {spec.name!r} has a size that only a weight file gives "
+                         f"({list(spec.shape)}); name it in the configuration to draw random weights")
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, spec.name))
     if spec.role == "int":

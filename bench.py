@@ -258,6 +258,77 @@ def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
     return times[len(times) // 2]
 
 
+
+# ----------------------------------------------------------------------------- another design
+# ``--design vilepel``: prefill and decode throughput of the Vilepel design at layer sizes that
+# resemble a real model's (random weights), beside Qwen2 at equal width, heads, feed-forward size
+# and layer count.  The default workload and its JSON line are untouched by this option.
+def vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top, expert_ff,
+                   layers, vocab=32768):
+    def latent():
+        return {"type": "latent_attention", "mixer": {
+            "heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank,
+            "scale": (dim + rot) ** -0.5, "mask": {"size": window},
+            "rot": {"base": 10000.0, "dims": rot}}}
+
+    def delta():
+        return {"type": "channel_delta", "mixer": {
+            "heads": heads, "kv_heads": heads, "dim": dim, "vdim": vdim, "conv": 4,
+            "decay_rank": 64, "gate_rank": 64}}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
+           "router": {"experts": experts, "top": top}}
+    kinds = [(latent, dense), (delta, moe), (latent, moe), (delta, dense)]
+    return {"architecture": "Vilepel", "width": width, "vocab": vocab, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "torch_dtype": "bfloat16",
+            "layers": [dict(kinds[i % 4][0](), mlp=kinds[i % 4][1]) for i in range(layers)]}
+
+
+DESIGN_SIZES = {
+    # width, heads, dim, rot, vdim, kv_rank, window, dense ff, experts, top, expert ff
+    "s": (1024, 8, 64, 32, 64, 256, 512, 2816, 16, 2, 704),
+    "m": (2048, 16, 128, 64, 128, 512, 1024, 5632, 32, 4, 1408),
+}
+
+
+def run_design(args) -> int:
+    import torch
+
+    from ginfer_b200.engine.llm import Engine
+    out = {"design": "vilepel", "beside": "qwen2 at equal width, heads, feed-forward and layers",
+           "dtype": "bfloat16", "data": "synthetic", "sizes": {}}
+    layers = args.layers or 8
+    for name in (args.size.split(",") if args.size else sorted(DESIGN_SIZES)):
+        width, heads, dim, rot, vdim, rank, window, ff, experts, top, eff = DESIGN_SIZES[name]
+        cfgs = {
+            "vilepel": vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top,
+                                      eff, layers),
+            "qwen2": dict(QWEN2_1P5B, num_hidden_layers=layers, hidden_size=width,
+                          num_attention_heads=heads, num_key_value_heads=max(1, heads // 4),
+                          head_dim=dim, intermediate_size=ff, vocab_size=32768,
+                          use_sliding_window=True, sliding_window=window, max_window_layers=0),
+        }
+        res = {}
+        for which, cfg in cfgs.items():
+            eng = Engine(config=cfg, weights_seed=0, dtype="bfloat16", max_num_batched_tokens=8192,
+                         max_num_seqs=64, max_seq_len=CONTEXT, kvcache_block_size=PAGE,
+                         num_kvcache_blocks=64 * (PROMPT + 256) // PAGE + PREFILL_TOKENS // PAGE + 64,
+                         enforce_eager=args.enforce_eager)
+            pre = prefill_timed(eng, PREFILL_TOKENS, reps=3, warmup=2, seed=3)
+            r = {"prefill_ms": round(pre, 3),
+                 "prefill_tok_per_s": round(PREFILL_TOKENS / pre * 1e3)}
+            for b in (1, 8, 64):
+                ms, _, _ = decode_device_timed(eng, b, args.steps, max(3, args.warmup), seed=b)
+                r[f"decode_b{b}_ms"] = round(ms, 4)
+                r[f"decode_b{b}_tok_per_s"] = round(b / ms * 1e3)
+            res[which] = r
+            del eng
+            torch.cuda.empty_cache()
+        out["sizes"][name] = dict(layers=layers, width=width, **res)
+    print(json.dumps(out))
+    return 0
+
+
 # ----------------------------------------------------------------------------- small workloads
 MICRO = ("gemm_gateup_m8", "gemm_down_m8", "gemm_lmhead_m8", "gemm_gateup_m2048", "gemm_qkv_m2048",
          "attn_decode_b8",
@@ -565,9 +636,14 @@ def main() -> int:
                     help="tokens a step of the long prompt in --scenario longctx (default 2,048)")
     ap.add_argument("--scenario", choices=SCENARIOS, default=None,
                     help="run a serving workload through the entry point instead of the benchmark")
+    ap.add_argument("--design", choices=["vilepel"], default=None,
+                    help="measure another design beside Qwen2 at equal size instead of the benchmark")
+    ap.add_argument("--size", default=None, help="with --design: sizes to run, e.g. s,m")
     args = ap.parse_args()
     if args.micro:
         return run_micro(args.micro)
+    if args.design:
+        return run_design(args)
     if args.scenario:
         if args.gpus != 1:
             print(json.dumps({"error": "this engine runs on one GPU", "n_gpus": args.gpus}))

@@ -28,10 +28,12 @@ def _mixer(cfg: VilepelConfig, kind: str, m) -> PartSpec:
             v_dim=m["vdim"], kv_rank=m["kv_rank"], scale=m["scale"], window=m["mask"]["size"],
             rotary_dims=m["rot"]["dims"], rotary_base=m["rot"]["base"], latent_eps=cfg.norm_eps,
             prefix="mix"))
+    # the inner sizes of the two low-rank projections are the tensors' own; a configuration may
+    # name them (``decay_rank``, ``gate_rank``) so that random weights can be drawn
     return PartSpec("channel_delta", dict(
         hidden_size=cfg.width, num_heads=m["heads"], num_kv_heads=m["kv_heads"],
         key_dim=m["dim"], v_dim=m["vdim"], conv_taps=m["conv"], out_norm_eps=cfg.norm_eps,
-        prefix="mix"))
+        decay_rank=m.get("decay_rank", -1), gate_rank=m.get("gate_rank", -1), prefix="mix"))
 
 
 def _feed_forward(cfg: VilepelConfig, mlp) -> PartSpec | None:

@@ -88,7 +88,7 @@ bool live_slot(Manager* m, int slot) {
 GF_EXPORT void* gf_cm_create(int num_groups, const int* pages_per_group, const int* windows,
                              int page_size, int max_num_seqs, int max_seq_len,
                              int32_t* const* tables) {
-  if (num_groups <= 0 || page_size <= 0 || max_num_seqs <= 0 || max_seq_len <= 0) return nullptr;
+  if (num_groups < 0 || page_size <= 0 || max_num_seqs <= 0 || max_seq_len <= 0) return nullptr;
   auto* m = new Manager();
   m->G = num_groups, m->page_size = page_size, m->max_seqs = max_num_seqs;
   m->max_seq_len = max_seq_len;

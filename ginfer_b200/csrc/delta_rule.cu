@@ -11,8 +11,8 @@
 //   delta_recurrence_kernel  per (request, head): S <- g * S (rows); u = beta (v - S^T k);
 //                            S <- S + k u^T; o = S^T q, token after token.  The columns of S are
 //                            independent: four lanes share a column (a quarter of the rows each, in
-//                            registers), a block holds 32 columns.  The next token's operands are
-//                            loaded while the current one is worked on.
+//                            registers), a block holds 16 or 32 columns.  The tokens' operands come
+//                            through two stages of shared memory, a chunk ahead (cp.async).
 //   delta_output_kernel      a warp a (token, head): o / rms(o) * w * sigmoid(gate).
 #include "common.cuh"
 
@@ -104,22 +104,40 @@ __global__ void delta_conv_state_kernel(const T* __restrict__ proj, int ld,
 }
 
 constexpr int kLanesPerColumn = 4;
-constexpr int kColumnsPerBlock = 32;
+constexpr int kMaxColumnsPerBlock = 32;
 
-template <int DPER>
-__global__ void __launch_bounds__(kLanesPerColumn * kColumnsPerBlock)
+__device__ __forceinline__ void copy_async_4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void copy_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// A block = (request, head, `cols` columns of S); blockDim.x = 4 * cols.  The tokens' k, q, g rows
+// (padded to Dp = 4 * DPER floats, the padding zero), the block's v columns and beta come through
+// two stages of shared memory, CHUNK tokens each, asked for one chunk ahead with cp.async.
+template <int DPER, int CHUNK>
+__global__ void __launch_bounds__(kLanesPerColumn * kMaxColumnsPerBlock)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
                         const float* __restrict__ v, const float* __restrict__ g,
                         const float* __restrict__ beta, float* __restrict__ state,
                         const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids,
                         DeltaDims dm, float* __restrict__ o) {
+  constexpr int Dp = kLanesPerColumn * DPER;
+  constexpr int kTok = 3 * Dp + kMaxColumnsPerBlock + 4;      // floats a token in a stage
+  extern __shared__ __align__(16) float stage[];               // [2][CHUNK][kTok]
+  const int cols = blockDim.x >> 2;
   const int b = blockIdx.x / dm.H, h = blockIdx.x - b * dm.H;
-  const int part = threadIdx.x & (kLanesPerColumn - 1);
-  const int col = blockIdx.y * kColumnsPerBlock + (threadIdx.x >> 2);
+  const int part = threadIdx.x & (kLanesPerColumn - 1), lc = threadIdx.x >> 2;
+  const int col0 = blockIdx.y * cols, col = col0 + lc;
   pdl_trigger();
-  pdl_wait();
   const int D = dm.D, Vd = dm.Vd;
-  const int row0 = part * DPER;                    // this lane's rows: row0 .. row0 + DPER - 1
+  for (int i = threadIdx.x; i < 2 * CHUNK * kTok; i += blockDim.x) stage[i] = 0.f;
+  __syncthreads();
+  pdl_wait();
+  const int row0 = part * DPER;
   const bool col_ok = col < Vd;
   const int cj = col_ok ? col : 0;
   const int kvh = h / (dm.H / dm.G);
@@ -129,49 +147,103 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   for (int i = 0; i < DPER; ++i) S[i] = (row0 + i < D) ? Sg[(size_t)(row0 + i) * Vd] : 0.f;
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
   const size_t GD = (size_t)dm.G * D, HD = (size_t)dm.H * D, HV = (size_t)dm.H * Vd;
-  float kc[DPER], qc[DPER], gc[DPER], vc, bc;
-  auto fetch = [&](int t, float (&k_)[DPER], float (&q_)[DPER], float (&g_)[DPER], float& v_,
-                   float& b_) {
-    const float* kp = kn + (size_t)t * GD + (size_t)kvh * D + row0;
-    const float* qp = qn + (size_t)t * GD + (size_t)kvh * D + row0;
-    const float* gp = g + (size_t)t * HD + (size_t)h * D + row0;
-#pragma unroll
-    for (int i = 0; i < DPER; ++i) {
-      const bool ok = row0 + i < D;
-      k_[i] = ok ? kp[i] : 0.f;
-      q_[i] = ok ? qp[i] : 0.f;
-      g_[i] = ok ? gp[i] : 0.f;
+  const int ncols = min(cols, Vd - col0);
+  // 16-byte copies where rows allow it (a thread keeps the same piece of every token), else 4-byte
+  const bool vec = (D & 3) == 0 && (Vd & 3) == 0 && (ncols & 3) == 0;
+  const int dq = D >> 2, pieces = 3 * dq + (ncols >> 2);
+  auto ask = [&](int chunk) {                      // the chunk's tokens into stage chunk & 1
+    float* st = stage + (size_t)(chunk & 1) * CHUNK * kTok;
+    const int ta = t0 + chunk * CHUNK, n = min(CHUNK, t1 - ta);
+    if (vec) {
+      for (int e = threadIdx.x; e < pieces; e += blockDim.x) {
+        const float* src;
+        int dst, step;                             // source floats from one token to the next
+        if (e < dq) src = kn + (size_t)ta * GD + (size_t)kvh * D + 4 * e, dst = 4 * e, step = (int)GD;
+        else if (e < 2 * dq)
+          src = qn + (size_t)ta * GD + (size_t)kvh * D + 4 * (e - dq), dst = Dp + 4 * (e - dq), step = (int)GD;
+        else if (e < 3 * dq)
+          src = g + (size_t)ta * HD + (size_t)h * D + 4 * (e - 2 * dq), dst = 2 * Dp + 4 * (e - 2 * dq),
+          step = (int)HD;
+        else
+          src = v + (size_t)ta * HV + (size_t)h * Vd + col0 + 4 * (e - 3 * dq),
+          dst = 3 * Dp + 4 * (e - 3 * dq), step = (int)HV;
+        for (int tt = 0; tt < n; ++tt)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                           smem_u32(st + (size_t)tt * kTok + dst)),
+                       "l"(src + (size_t)tt * step)
+                       : "memory");
+      }
+      if (threadIdx.x < n)
+        copy_async_4(st + (size_t)threadIdx.x * kTok + 3 * Dp + kMaxColumnsPerBlock,
+                     beta + (size_t)(ta + threadIdx.x) * dm.H + h);
+    } else {
+      const int per = 3 * D + ncols + 1;
+      for (int i = threadIdx.x; i < n * per; i += blockDim.x) {
+        const int tt = i / per, e = i - tt * per;
+        const size_t t = (size_t)(ta + tt);
+        float* dst = st + (size_t)tt * kTok;
+        if (e < D) copy_async_4(dst + e, kn + t * GD + (size_t)kvh * D + e);
+        else if (e < 2 * D) copy_async_4(dst + Dp + (e - D), qn + t * GD + (size_t)kvh * D + (e - D));
+        else if (e < 3 * D) copy_async_4(dst + 2 * Dp + (e - 2 * D), g + t * HD + (size_t)h * D + (e - 2 * D));
+        else if (e < 3 * D + ncols)
+          copy_async_4(dst + 3 * Dp + (e - 3 * D), v + t * HV + (size_t)h * Vd + col0 + (e - 3 * D));
+        else copy_async_4(dst + 3 * Dp + kMaxColumnsPerBlock, beta + t * dm.H + h);
+      }
     }
-    v_ = v[(size_t)t * HV + (size_t)h * Vd + cj];
-    b_ = beta[(size_t)t * dm.H + h];
+    copy_async_commit();
   };
-  if (t0 < t1) fetch(t0, kc, qc, gc, vc, bc);
-  for (int t = t0; t < t1; ++t) {
-    float kx[DPER], qx[DPER], gx[DPER], vx = 0.f, bx = 0.f;
-    if (t + 1 < t1) fetch(t + 1, kx, qx, gx, vx, bx);
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < DPER; ++i) {
-      S[i] *= gc[i];
-      dot = fmaf(S[i], kc[i], dot);
+  const int nchunks = (t1 - t0 + CHUNK - 1) / CHUNK;
+  if (nchunks > 0) ask(0);
+  for (int c = 0; c < nchunks; ++c) {
+    if (c + 1 < nchunks) {
+      ask(c + 1);
+      copy_async_wait<1>();
+    } else {
+      copy_async_wait<0>();
     }
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-    const float u = bc * (vc - dot);
-    float out = 0.f;
+    __syncthreads();
+    const float* st = stage + (size_t)(c & 1) * CHUNK * kTok;
+    const int ta = t0 + c * CHUNK, n = min(CHUNK, t1 - ta);
+    for (int tt = 0; tt < n; ++tt) {
+      const float* tok = st + (size_t)tt * kTok;
+      const float4* k4 = reinterpret_cast<const float4*>(tok + row0);
+      const float4* q4 = reinterpret_cast<const float4*>(tok + Dp + row0);
+      const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * Dp + row0);
+      const float vc = tok[3 * Dp + lc], bc = tok[3 * Dp + kMaxColumnsPerBlock];
+      float kc[DPER];
+      float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < DPER; ++i) {
-      S[i] = fmaf(kc[i], u, S[i]);
-      out = fmaf(S[i], qc[i], out);
-    }
-    out += __shfl_xor_sync(0xffffffffu, out, 1);
-    out += __shfl_xor_sync(0xffffffffu, out, 2);
-    if (part == 0 && col_ok) o[(size_t)t * HV + (size_t)h * Vd + col] = out;
-    if (t + 1 < t1) {
+      for (int i = 0; i < DPER / 4; ++i) {
+        const float4 kk = k4[i], gg = g4[i];
+        kc[4 * i] = kk.x, kc[4 * i + 1] = kk.y, kc[4 * i + 2] = kk.z, kc[4 * i + 3] = kk.w;
+        S[4 * i] *= gg.x, S[4 * i + 1] *= gg.y, S[4 * i + 2] *= gg.z, S[4 * i + 3] *= gg.w;
+      }
+      float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DPER; ++i) kc[i] = kx[i], qc[i] = qx[i], gc[i] = gx[i];
-      vc = vx, bc = bx;
+      for (int i = 0; i < DPER; ++i) d4[i & 3] = fmaf(S[i], kc[i], d4[i & 3]);
+      dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      const float u = bc * (vc - dot);
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < DPER / 4; ++i) {
+        const float4 qq = q4[i];
+        S[4 * i] = fmaf(kc[4 * i], u, S[4 * i]);
+        S[4 * i + 1] = fmaf(kc[4 * i + 1], u, S[4 * i + 1]);
+        S[4 * i + 2] = fmaf(kc[4 * i + 2], u, S[4 * i + 2]);
+        S[4 * i + 3] = fmaf(kc[4 * i + 3], u, S[4 * i + 3]);
+        o4[0] = fmaf(S[4 * i], qq.x, o4[0]);
+        o4[1] = fmaf(S[4 * i + 1], qq.y, o4[1]);
+        o4[2] = fmaf(S[4 * i + 2], qq.z, o4[2]);
+        o4[3] = fmaf(S[4 * i + 3], qq.w, o4[3]);
+      }
+      float out = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+      out += __shfl_xor_sync(0xffffffffu, out, 1);
+      out += __shfl_xor_sync(0xffffffffu, out, 2);
+      if (part == 0 && col_ok) o[(size_t)(ta + tt) * HV + (size_t)h * Vd + col] = out;
     }
+    __syncthreads();                               // the stage is free for the chunk after next
   }
   if (col_ok) {
 #pragma unroll
@@ -263,17 +335,22 @@ GF_EXPORT int gf_delta_recurrence(const float* qn, const float* kn, const float*
   if (H % G) return -3;
   const DeltaDims dm = dims_of(H, G, D, Vd, 1, state_stride, 0);
   auto st = (cudaStream_t)stream;
-  const dim3 grid(B * H, (Vd + kColumnsPerBlock - 1) / kColumnsPerBlock);
-  const dim3 block(kLanesPerColumn * kColumnsPerBlock);
-#define GF_GO(DPER)                                                                            \
-  if (D <= kLanesPerColumn * DPER)                                                             \
-    return launch_kernel(delta_recurrence_kernel<DPER>, grid, block, 0, st, qn, kn, v, g, beta, \
-                         state, cu_seqlens, slot_ids, dm, o)
-  GF_GO(4);
-  GF_GO(8);
-  GF_GO(16);
-  GF_GO(32);
-  GF_GO(64);
+  // few (request, head) pairs: narrower blocks, so that more SMs take part
+  const int cols = (long long)B * H * ((Vd + 31) / 32) < 148 ? 16 : 32;
+  const dim3 grid(B * H, (Vd + cols - 1) / cols);
+  const dim3 block(kLanesPerColumn * cols);
+#define GF_GO(DPER, CHUNK)                                                                        \
+  if (D <= kLanesPerColumn * DPER) {                                                              \
+    const size_t smem = (size_t)2 * CHUNK * (3 * kLanesPerColumn * DPER + kMaxColumnsPerBlock + 4) * \
+                        sizeof(float);                                                            \
+    return launch_kernel(delta_recurrence_kernel<DPER, CHUNK>, grid, block, smem, st, qn, kn, v, g, \
+                         beta, state, cu_seqlens, slot_ids, dm, o);                               \
+  }
+  GF_GO(4, 8)
+  GF_GO(8, 8)
+  GF_GO(16, 8)
+  GF_GO(32, 8)
+  GF_GO(64, 4)
 #undef GF_GO
   return -3;
 }

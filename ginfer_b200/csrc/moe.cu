@@ -7,7 +7,8 @@
 //   moe_plan_kernel     one block: (token, choice) pairs counted per expert, the experts' ranges in
 //                       the sorted order, each pair's place, and the list of row tiles (expert,
 //                       first row) that the grouped products walk over.
-//   moe_gemm_kernel     grouped product over the sorted pairs, a block a (row tile, column tile):
+//   moe_gemm_mma_kernel the grouped products of the bf16 path, on the tensor cores (see there).
+//   moe_gemm_kernel     (32-bit path, and sizes the other refuses) grouped product over the sorted pairs, a block a (row tile, column tile):
 //                       FIRST: rows gathered from the tokens, W = the expert's row-interleaved
 //                       gate/up matrix, epilogue = clamped sigmoid-gated GLU; else rows = the first
 //                       product's output, W = the expert's down matrix, fp32 out.  The reduction
@@ -205,6 +206,132 @@ moe_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, int N
   }
 }
 
+
+// ---- the same grouped products on the tensor cores (bf16 operands, fp32 accumulation) -----------
+// Tile 64 rows x 128 columns x 32 of the reduction; 8 warps as 2 x 4, a warp 32 x 32 (2 x 4
+// mma.sync.m16n8k16 a k-step).  Operand tiles come through three stages of shared memory by 16-byte
+// cp.async (rows 40 halves apart: fragment loads meet every bank once); rows past an expert's range
+// are zero-filled.  Needs K and the row strides to be multiples of 8 and 16-byte aligned bases.
+constexpr int kTM = 64, kTN = 128, kTK = 32, kTStages = 3, kTLd = kTK + 8;
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n)
+               : "memory");
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <bool FIRST>
+__global__ void __launch_bounds__(256)
+moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w,
+                    int N, int K, const int* __restrict__ offsets,
+                    const int* __restrict__ pair_of_pos, int top,
+                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                    const int* __restrict__ num_tiles, void* __restrict__ out_, float limit,
+                    float alpha, float up_shift) {
+  __shared__ __align__(16) __nv_bfloat16 As[kTStages][kTM][kTLd];
+  __shared__ __align__(16) __nv_bfloat16 Ws[kTStages][kTN][kTLd];
+  __shared__ int src_row[kTM];
+  pdl_trigger();
+  pdl_wait();
+  if ((int)blockIdx.x >= num_tiles[0]) return;
+  const int e = tile_expert[blockIdx.x], row0 = tile_row0[blockIdx.x];
+  const int rows = min(kTM, offsets[e + 1] - row0);
+  const int n0 = blockIdx.y * kTN;
+  const __nv_bfloat16* we = w + (size_t)e * N * K;
+  if (threadIdx.x < kTM) {
+    const int s = row0 + threadIdx.x;
+    src_row[threadIdx.x] = threadIdx.x < rows ? (FIRST ? pair_of_pos[s] / top : s) : -1;
+  }
+  __syncthreads();
+  const int nk = (K + kTK - 1) / kTK;
+  auto ask = [&](int kb) {
+    const int st = kb % kTStages, k0 = kb * kTK;
+    {                                              // A: 64 rows x 4 pieces of 8
+      const int r = threadIdx.x >> 2, c = (threadIdx.x & 3) * 8;
+      const int sr = src_row[r];
+      const bool ok = sr >= 0 && k0 + c < K;
+      cp_async_16(&As[st][r][c], ok ? a + (size_t)sr * lda + k0 + c : a, ok);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {                  // W: 128 rows x 4 pieces of 8
+      const int id = threadIdx.x + 256 * i;
+      const int r = id >> 2, c = (id & 3) * 8;
+      const bool ok = n0 + r < N && k0 + c < K;
+      cp_async_16(&Ws[st][r][c], ok ? we + (size_t)(n0 + r) * K + k0 + c : we, ok);
+    }
+  };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wm = warp >> 2, wn = warp & 3;         // the warp's 32 x 32 part
+  const int g = lane >> 2, t = lane & 3;
+  float acc[2][4][4] = {};
+  for (int s = 0; s < kTStages - 1; ++s) {
+    if (s < nk) ask(s);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (int kb = 0; kb < nk; ++kb) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kTStages - 2) : "memory");
+    __syncthreads();                               // stage kb has landed; stage kb - 1 is free
+    if (kb + kTStages - 1 < nk) ask(kb + kTStages - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int st = kb % kTStages;
+#pragma unroll
+    for (int kk = 0; kk < kTK; kk += 16) {
+      uint32_t af[2][4], bfr[4][2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const __nv_bfloat16* base = &As[st][wm * 32 + i * 16 + g][kk + 2 * t];
+        af[i][0] = *reinterpret_cast<const uint32_t*>(base);
+        af[i][1] = *reinterpret_cast<const uint32_t*>(base + 8 * kTLd);
+        af[i][2] = *reinterpret_cast<const uint32_t*>(base + 8);
+        af[i][3] = *reinterpret_cast<const uint32_t*>(base + 8 * kTLd + 8);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat16* base = &Ws[st][wn * 32 + j * 8 + g][kk + 2 * t];
+        bfr[j][0] = *reinterpret_cast<const uint32_t*>(base);
+        bfr[j][1] = *reinterpret_cast<const uint32_t*>(base + 8);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bfr[j]);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  // c0, c1: row g, columns 2t, 2t + 1; c2, c3: row g + 8
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = wm * 32 + i * 16 + g + 8 * hh;
+      if (r >= rows) continue;
+      const size_t s = (size_t)(row0 + r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + wn * 32 + j * 8 + 2 * t;
+        const float c0 = acc[i][j][2 * hh], c1 = acc[i][j][2 * hh + 1];
+        if (FIRST) {
+          if (n < N) {
+            const float gt = to_f32(from_f32<__nv_bfloat16>(c0)), up = to_f32(from_f32<__nv_bfloat16>(c1));
+            ((__nv_bfloat16*)out_)[s * (N / 2) + n / 2] =
+                from_f32<__nv_bfloat16>(clamped_glu(gt, up, limit, alpha, up_shift));
+          }
+        } else {
+          float* out = (float*)out_ + s * N;
+          if (n < N) out[n] = c0;
+          if (n + 1 < N) out[n + 1] = c1;
+        }
+      }
+    }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
                                    const float* __restrict__ wgt, int top, int N,
@@ -227,7 +354,8 @@ using bf = __nv_bfloat16;
 
 GF_DEFINE_PDL_SWITCH
 
-GF_EXPORT int gf_moe_tile_rows() { return kBM; }
+// Rows of a tile: of the plain kernel (tensor_cores == 0) or of the tensor-core kernel.
+GF_EXPORT int gf_moe_tile_rows(int tensor_cores) { return tensor_cores ? kTM : kBM; }
 
 GF_EXPORT int gf_moe_route(const float* logits, int T, int E, int top, int renorm, int* idx,
                            float* wgt, void* stream) {
@@ -237,13 +365,14 @@ GF_EXPORT int gf_moe_route(const float* logits, int T, int E, int top, int renor
                        logits, T, E, top, renorm, idx, wgt);
 }
 
-GF_EXPORT int gf_moe_plan(const int* idx, int P, int E, int* offsets, int* pos_of_pair,
-                          int* pair_of_pos, int* tile_expert, int* tile_row0, int* num_tiles,
-                          void* stream) {
+GF_EXPORT int gf_moe_plan(const int* idx, int P, int E, int tile_rows, int* offsets,
+                          int* pos_of_pair, int* pair_of_pos, int* tile_expert, int* tile_row0,
+                          int* num_tiles, void* stream) {
   if (P <= 0) return 0;
-  if (E > kMaxExperts) return -3;
+  if (E > kMaxExperts || (tile_rows != kBM && tile_rows != kTM)) return -3;
   return launch_kernel(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, idx, P, E,
-                       kBM, offsets, pos_of_pair, pair_of_pos, tile_expert, tile_row0, num_tiles);
+                       tile_rows, offsets, pos_of_pair, pair_of_pos, tile_expert, tile_row0,
+                       num_tiles);
 }
 
 // first != 0: gate/up product with the activation; out [P, N / 2] (dtype).  Else down: out fp32.
@@ -251,9 +380,20 @@ GF_EXPORT int gf_moe_gemm(const void* a, int lda, const void* w, int N, int K, c
                           const int* pair_of_pos, int top, const int* tile_expert,
                           const int* tile_row0, const int* num_tiles, int max_tiles, void* out,
                           int first, float limit, float alpha, float up_shift, int dtype,
-                          void* stream) {
+                          int tensor_cores, void* stream) {
   if (max_tiles <= 0) return 0;
   auto st = (cudaStream_t)stream;
+  if (tensor_cores) {
+    if (dtype != GF_BF16 || K % 8 || lda % 8 || (uintptr_t)a % 16 || (uintptr_t)w % 16) return -3;
+    const dim3 tgrid(max_tiles, (N + kTN - 1) / kTN), tblock(256);
+    if (first)
+      return launch_kernel(moe_gemm_mma_kernel<true>, tgrid, tblock, 0, st, (const bf*)a, lda,
+                           (const bf*)w, N, K, offsets, pair_of_pos, top, tile_expert, tile_row0,
+                           num_tiles, out, limit, alpha, up_shift);
+    return launch_kernel(moe_gemm_mma_kernel<false>, tgrid, tblock, 0, st, (const bf*)a, lda,
+                         (const bf*)w, N, K, offsets, pair_of_pos, top, tile_expert, tile_row0,
+                         num_tiles, out, limit, alpha, up_shift);
+  }
   const dim3 grid(max_tiles, (N + kBN - 1) / kBN), block(256);
 #define GF_GO(T, FIRST)                                                                          \
   return launch_kernel(moe_gemm_kernel<T, FIRST>, grid, block, 0, st, (const T*)a, lda,          \

@@ -8,14 +8,19 @@ import torch
 
 from . import _code, _cuda, _fn, _ok, _p, _stream, load_library
 
-_tile_rows = None
+_tile_rows: dict = {}
 
 
-def tile_rows() -> int:
-    global _tile_rows
-    if _tile_rows is None:
-        _tile_rows = int(load_library("moe").gf_moe_tile_rows())
-    return _tile_rows
+def tile_rows(tensor_cores: bool) -> int:
+    if tensor_cores not in _tile_rows:
+        _tile_rows[tensor_cores] = int(load_library("moe").gf_moe_tile_rows(int(tensor_cores)))
+    return _tile_rows[tensor_cores]
+
+
+def on_tensor_cores(dtype: torch.dtype, *reductions: int) -> bool:
+    """Whether the grouped products of this dtype and these reduction sizes run on the tensor-core
+    kernel (bf16, sizes that 16-byte copies can fetch) or on the plain one."""
+    return dtype == torch.bfloat16 and all(k % 8 == 0 for k in reductions)
 
 
 def route(logits: torch.Tensor, top: int, renormalize: bool):
@@ -38,12 +43,14 @@ def route(logits: torch.Tensor, top: int, renormalize: bool):
 class Plan:
     """Where every (token, choice) pair sits once the pairs are sorted by expert."""
 
-    def __init__(self, idx: torch.Tensor, num_experts: int):
+    def __init__(self, idx: torch.Tensor, num_experts: int, tensor_cores: bool = False):
         T, top = idx.shape
+        self.tensor_cores = bool(tensor_cores)
+        rows = tile_rows(self.tensor_cores)
         P = T * top
         dev = idx.device
         self.pairs, self.top, self.num_experts = P, top, num_experts
-        self.max_tiles = -(-P // tile_rows()) + num_experts
+        self.max_tiles = -(-P // rows) + num_experts
         ints = torch.empty(num_experts + 1 + 2 * P + 2 * self.max_tiles + 1, dtype=torch.int32,
                            device=dev)
         at = 0
@@ -56,8 +63,8 @@ class Plan:
         self.offsets, self.pos_of_pair, self.pair_of_pos = take(num_experts + 1), take(P), take(P)
         self.tile_expert, self.tile_row0 = take(self.max_tiles), take(self.max_tiles)
         self.num_tiles = take(1)
-        f = _fn("moe", "gf_moe_plan", [c_void_p, c_int, c_int] + [c_void_p] * 7)
-        rc = f(_p(idx), P, num_experts, _p(self.offsets), _p(self.pos_of_pair),
+        f = _fn("moe", "gf_moe_plan", [c_void_p, c_int, c_int, c_int] + [c_void_p] * 7)
+        rc = f(_p(idx), P, num_experts, rows, _p(self.offsets), _p(self.pos_of_pair),
                _p(self.pair_of_pos), _p(self.tile_expert), _p(self.tile_row0), _p(self.num_tiles),
                _stream())
         _ok(rc, "moe_plan")
@@ -90,11 +97,11 @@ def _gemm(a, w, plan, out, first, limit, alpha, up_shift):
     f = _fn("moe", "gf_moe_gemm",
             [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
              c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float, c_int,
-             c_void_p])
+             c_int, c_void_p])
     _ok(f(_p(a), a.stride(0), _p(w), w.shape[1], w.shape[2], _p(plan.offsets),
           _p(plan.pair_of_pos), plan.top, _p(plan.tile_expert), _p(plan.tile_row0),
           _p(plan.num_tiles), plan.max_tiles, _p(out), int(first), float(limit), float(alpha),
-          float(up_shift), _code(a.dtype), _stream()), "moe_gemm")
+          float(up_shift), _code(a.dtype), int(plan.tensor_cores), _stream()), "moe_gemm")
 
 
 def combine(y: torch.Tensor, plan: Plan, weights: torch.Tensor, num_tokens: int) -> torch.Tensor:

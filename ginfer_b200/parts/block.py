@@ -103,8 +103,7 @@ class OutputNormBlock(Block):
     the kernel that adds a normed output to it also writes the sum rounded to the activation
     dtype, which is what the next sublayer's products read (it travels to the next block in
     ``ctx.extras["act_copy"]``; a block that does not find its own ``x`` there rounds it anew).
-    A feed-forward that routes in 32-bit finds the stream in ``ctx.extras["stream"]``.  A layer
-    without a feed-forward is the first line alone."""
+    A layer without a feed-forward is the first line alone."""
 
     def __init__(self, layer_spec):
         self.spec = layer_spec
@@ -139,7 +138,6 @@ class OutputNormBlock(Block):
         a = self.mixer.forward(h, ctx, cache)
         x, h = self.mixer_norm.add_output(x, a, ctx.dtype)
         if self.feed_forward is not None:
-            ctx.extras["stream"] = x
             m = self.feed_forward.forward(h, ctx)
             x, h = self.feed_forward_norm.add_output(x, m, ctx.dtype)
         ctx.extras["act_copy"] = (x, h)

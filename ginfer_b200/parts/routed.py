@@ -1,7 +1,8 @@
 """Routed feed-forward (mixture of experts).
 
-Router logits ``z = h W_r^T`` in 32-bit from the fp32 stream, scores ``softmax(z)`` over ALL
-experts, the ``top_k`` largest chosen; a token's output is the sum of the chosen experts' outputs
+Router logits ``z = h W_r^T`` in 32-bit (float32 path: from the fp32 stream; bfloat16 path: from
+the bfloat16 rounding of ``h`` and the bfloat16 router matrix, whose products are exact in 32-bit
+and are added up in 32-bit by the tensor cores), scores ``softmax(z)`` over ALL experts, the ``top_k`` largest chosen; a token's output is the sum of the chosen experts' outputs
 weighted by their scores (as they are, or renormalised over the chosen ones with
 ``renormalize``).  An expert is a clamped GLU (see :class:`ClampedGLU`) without biases, stored as
 ``<prefix>.e<i>.gate|up|down``.
@@ -37,7 +38,7 @@ class RoutedGLU(FeedForward):
             p = f"{self.prefix}e{e}."
             out += [TensorSpec(p + "gate", (f, h)), TensorSpec(p + "up", (f, h)),
                     TensorSpec(p + "down", (h, f))]
-        out.append(TensorSpec(self.prefix + "router", (self.E, h), "f32"))
+        out.append(TensorSpec(self.prefix + "router", (self.E, h)))
         return out
 
     def load(self, tensors, dtype, device):
@@ -47,15 +48,14 @@ class RoutedGLU(FeedForward):
         self.w_gate_up = torch.stack(gu).contiguous()                       # [E, 2 F, H]
         self.w_down = torch.stack([tensors[f"{self.prefix}e{e}.down"]
                                    for e in range(self.E)]).contiguous()    # [E, H, F]
-        self.router = ops.Linear(tensors[self.prefix + "router"].float())
+        self.router = ops.Linear(tensors[self.prefix + "router"], None, out_dtype=torch.float32)
 
     def forward(self, x, ctx):
         T = x.shape[0]
-        stream = ctx.extras.get("stream")
-        h32 = stream if (stream is not None and stream.shape == x.shape
-                         and stream.dtype == torch.float32) else x.float()
-        idx, wgt = moe.route(self.router(h32), self.top, self.renormalize)
-        plan = moe.Plan(idx, self.E)
+        idx, wgt = moe.route(self.router(x), self.top, self.renormalize)
+        plan = moe.Plan(idx, self.E, moe.on_tensor_cores(x.dtype, self.hidden_size,
+                                                         self.intermediate_size)
+                        and x.stride(0) % 8 == 0)
         y = moe.grouped_glu(x, self.w_gate_up, plan, self.limit, self.alpha, self.up_shift)
         return moe.combine(moe.grouped_down(y, self.w_down, plan), plan, wgt, T)
 

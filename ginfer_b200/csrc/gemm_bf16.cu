@@ -11,7 +11,8 @@
 // tensor memory and issues tcgen05.mma (one thread), releasing stages with tcgen05.commit; warps
 // 2..5 read the accumulator back with tcgen05.ld and run the epilogue:
 //   EPI_STORE  out = acc (+ bias[n]) as bf16 or fp32
-//   EPI_SILU   W rows are interleaved (gate_i, up_i): out[m, i] = silu(bf16(gate)) * bf16(up)
+//   EPI_SILU   W rows are interleaved (gate_i, up_i): out[m, i] = silu(bf16(gate)) * bf16(up), or the
+//              clamped sigmoid-gated form when `bias` holds its three constants (see silu_mul)
 //   EPI_RESID  s = resid + acc (+ bias[n]) in fp32, the new residual stream; beside it
 //              bf16(s * gamma[n]) (the operand of the product behind the next RMS norm) and, per
 //              token, this CTA's share of sum_n s^2
@@ -102,9 +103,18 @@ __device__ __forceinline__ float gamma_at(const GemmExtra& ex, int n) {
   return ex.gamma_f32 ? reinterpret_cast<const float*>(ex.gamma)[n]
                       : __bfloat162float(reinterpret_cast<const bf16*>(ex.gamma)[n]);
 }
-__device__ __forceinline__ float silu_mul(float g, float u) {
-  const float gg = __bfloat162float(__float2bfloat16_rn(g));
-  const float uu = __bfloat162float(__float2bfloat16_rn(u));
+// The gated activation of EPI_SILU.  `act` null: silu(gate) * up.  Else act = {limit, alpha, shift}
+// (the kernel's `bias` argument, which EPI_SILU has no other use for):
+// min(gate, limit) * sigmoid(alpha * min(gate, limit)) * (clamp(up, -limit, limit) + shift).
+__device__ __forceinline__ float silu_mul(float g, float u, const float* __restrict__ act) {
+  float gg = __bfloat162float(__float2bfloat16_rn(g));
+  float uu = __bfloat162float(__float2bfloat16_rn(u));
+  if (act) {
+    const float limit = __ldg(act), alpha = __ldg(act + 1), shift = __ldg(act + 2);
+    gg = fminf(gg, limit);
+    uu = fminf(fmaxf(uu, -limit), limit);
+    return gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + shift);
+  }
   return gg * (1.0f / (1.0f + expf(-gg))) * uu;
 }
 
@@ -156,7 +166,7 @@ __device__ __forceinline__ void epilogue16(float (&v)[16], OUT* __restrict__ out
         const float g = (lane & 1) ? other : v[j], u = (lane & 1) ? v[j] : other;
         const int pair = n >> 1;
         if ((n | 1) < N && m_base + j < M)
-          store_out<OUT>(out + (size_t)(m_base + j) * ldo + pair, silu_mul(g, u));
+          store_out<OUT>(out + (size_t)(m_base + j) * ldo + pair, silu_mul(g, u, bias));
       }
     }
   }
@@ -267,7 +277,7 @@ __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* recv, 
         if (EPI == EPI_SILU) {
           // rows are (gate, up) pairs: two results
           const int pair = n >> 1;
-          const float r0 = silu_mul(v[0], v[1]), r1 = silu_mul(v[2], v[3]);
+          const float r0 = silu_mul(v[0], v[1], bias), r1 = silu_mul(v[2], v[3], bias);
           OUT* dst = out + (size_t)m * ldo + pair;
           if (n + 1 < N) store_out<OUT>(dst, r0);
           if (n + 3 < N) store_out<OUT>(dst + 1, r1);

@@ -505,9 +505,16 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
             float z[2];
 #pragma unroll
             for (int w = 0; w < 2; ++w) {
-              const float g = __bfloat162float(__float2bfloat16_rn(v[4 * u + 2 * w]));
-              const float up = __bfloat162float(__float2bfloat16_rn(v[4 * u + 2 * w + 1]));
-              z[w] = g * (1.0f / (1.0f + expf(-g))) * up;
+              float g = __bfloat162float(__float2bfloat16_rn(v[4 * u + 2 * w]));
+              float up = __bfloat162float(__float2bfloat16_rn(v[4 * u + 2 * w + 1]));
+              if (bias) {        // {limit, alpha, shift} of the clamped sigmoid-gated form
+                const float limit = __ldg(bias), alpha = __ldg(bias + 1), shift = __ldg(bias + 2);
+                g = fminf(g, limit);
+                up = fminf(fmaxf(up, -limit), limit);
+                z[w] = g * (1.0f / (1.0f + expf(-alpha * g))) * (up + shift);
+              } else {
+                z[w] = g * (1.0f / (1.0f + expf(-g))) * up;
+              }
             }
             p[u] = __floats2bfloat162_rn(z[0], z[1]);
           }
@@ -561,7 +568,9 @@ GF_DEFINE_PDL_SWITCH
 
 // x [M, K] bf16 (row stride ldx), w [N, K] bf16 contiguous, bias fp32 [N] or null.
 // epi 0: out [M, N] (row stride ldo) bf16 or fp32 = x w^T (+ bias); epi 2: w rows interleaved
-// (gate_i, up_i), out [M, N / 2] bf16 = silu(gate) * up.  `ctas`: CTAs to launch (0: one an SM).
+// (gate_i, up_i), out [M, N / 2] bf16 = silu(gate) * up, or, when `bias` holds {limit, alpha, shift},
+// min(gate, limit) * sigmoid(alpha * min(gate, limit)) * (clamp(up, -limit, limit) + shift).
+// `ctas`: CTAs to launch (0: one an SM).
 // -6: a shape or alignment this kernel does not take (the caller uses another product).
 // `pair`: on CTA pairs (tiles of 256 tokens; see the top of the file).
 GF_EXPORT int gf_gemm_prefill(const void* x, int ldx, const void* w, const void* bias, void* out,
@@ -597,8 +606,8 @@ GF_EXPORT int gf_gemm_prefill(const void* x, int ldx, const void* w, const void*
   auto st = (cudaStream_t)stream;
   if (pair) {
     if (epi == PEPI_GATED)
-      return launch_prefill<PEPI_GATED, bf16, true>(mx, mw, nullptr, out, ldo, M, N, K, err, ctas,
-                                                    st);
+      return launch_prefill<PEPI_GATED, bf16, true>(mx, mw, (const float*)bias, out, ldo, M, N, K,
+                                                    err, ctas, st);
     if (out_f32)
       return launch_prefill<PEPI_STORE, float, true>(mx, mw, (const float*)bias, out, ldo, M, N, K,
                                                      err, ctas, st);
@@ -606,7 +615,8 @@ GF_EXPORT int gf_gemm_prefill(const void* x, int ldx, const void* w, const void*
                                                   err, ctas, st);
   }
   if (epi == PEPI_GATED)
-    return launch_prefill<PEPI_GATED, bf16>(mx, mw, nullptr, out, ldo, M, N, K, err, ctas, st);
+    return launch_prefill<PEPI_GATED, bf16>(mx, mw, (const float*)bias, out, ldo, M, N, K, err, ctas,
+                                            st);
   if (out_f32)
     return launch_prefill<PEPI_STORE, float>(mx, mw, (const float*)bias, out, ldo, M, N, K, err,
                                              ctas, st);

@@ -169,15 +169,17 @@ __global__ void latent_attention_kernel(const float* __restrict__ q_lat,   // [H
 
 
 // ---- the same attention on the tensor cores (bf16 cache) ----------------------------------------
-// A block = one token x 16 heads (the rows of an m16n8k16 tile), four warps.  Keys come in tiles of
+// A block = one token x 16 heads (the rows of an m16n8k16 tile), eight warps.  Keys come in tiles of
 // 64 through two stages of shared memory (16-byte cp.async straight from the pages, rows past the
-// token's position zero-filled).  Scores: warp w takes keys 16 w .. 16 w + 15 of the tile over the
-// whole reduction [c | r]; the row maxima meet in shared memory; P goes to shared memory as bf16 and
-// every warp multiplies it with its quarter of the latent channels, read from the SAME tile (the
-// values are the first C channels of the keys) through transposing ldmatrix loads.  Running
-// maximum, sums and the output accumulator are fp32; the query is rounded to bf16 once.
-// Needs C % 32 == 0, R % 16 == 0, C <= 32 * 4 * NT / 4 (NT column tiles of 8 a warp).
+// token's position zero-filled).  Scores: warp w takes keys 8 w .. 8 w + 7 of the tile over the whole
+// reduction [c | r] (two accumulators, even and odd k-steps, so that the products do not wait for
+// one another); the row maxima meet in shared memory; P goes to shared memory as bf16 and every
+// warp multiplies it with its share of the latent channels, read from the SAME tile (the values are
+// the first C channels of the keys) through transposing ldmatrix loads.  Running maximum, sums and
+// the output accumulator are fp32; the query is rounded to bf16 once.
+// Needs C % 16 == 0, R % 16 == 0, C <= 64 * NT (NT column tiles of 8 a warp).
 constexpr int kMmaTile = 64;
+constexpr int kMmaWarps = 8;
 
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
   const int n = valid ? 16 : 0;
@@ -191,13 +193,28 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+               : "=r"(r[0]), "=r"(r[1])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+               : "=r"(r[0]), "=r"(r[1])
+               : "r"(smem_u32(p)));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
 template <int NT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kMmaWarps * 32)
 latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot,
                             const bf16* __restrict__ c_pages, const bf16* __restrict__ r_pages,
                             const int* __restrict__ block_table, int table_stride,
@@ -211,7 +228,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][ld]
   bf16* Ks = Qs + 16 * ld;                                   // [2][64][ld]
   bf16* Ps = Ks + 2 * kMmaTile * ld;                         // [16][pld]
-  float* red = reinterpret_cast<float*>(Ps + 16 * pld);      // [4][16]
+  float* red = reinterpret_cast<float*>(Ps + 16 * pld);      // [8][16]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
   const int t = blockIdx.x, h0 = blockIdx.y * 16;
   pdl_trigger();
@@ -230,11 +247,11 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   const int nchunk = Dk >> 3;
   auto ask = [&](int tile) {
     bf16* dst = Ks + (size_t)(tile & 1) * kMmaTile * ld;
-    const int j = threadIdx.x >> 1;                          // two threads a key
+    const int j = threadIdx.x >> 2;                          // four threads a key
     const int c = lo + tile * kMmaTile + j;
     const bool ok = c <= p;
     const size_t slot = ok ? (size_t)tbl[c / page_size] * page_size + c % page_size : 0;
-    for (int i = threadIdx.x & 1; i < nchunk; i += 2) {
+    for (int i = threadIdx.x & 3; i < nchunk; i += 4) {
       const int d = i << 3;
       const bf16* src = d < C ? c_pages + slot * C + d : r_pages + slot * R + (d - C);
       cp_async_16(dst + (size_t)j * ld + d, src, ok);
@@ -242,11 +259,16 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   const int ntiles = (p - lo) / kMmaTile + 1;
-  const int ntw = C >> 5;                                    // column tiles of 8 this warp owns
+  const int ctiles = C >> 3;                                 // column tiles of 8 in all
+  const int ntw = (ctiles + kMmaWarps - 1) / kMmaWarps;      // of which this warp owns up to ntw
   float o[NT][4];
 #pragma unroll
   for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, lsum[2] = {0.f, 0.f};
+  // ldmatrix addresses: A (16 rows x 16 k): lanes 0-15 rows, lanes 16-31 the second 8 k;
+  // B of the scores (8 keys x 16 k): lanes 0-7 keys at k, lanes 8-15 the same keys at k + 8
+  const int a_row = lane & 15, a_col = (lane >> 4) << 3;
+  const int b_row = 8 * warp + (lane & 7), b_col = ((lane >> 3) & 1) << 3;
   ask(0);
   for (int it = 0; it < ntiles; ++it) {
     if (it + 1 < ntiles) {
@@ -257,33 +279,35 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     }
     __syncthreads();
     const bf16* K = Ks + (size_t)(it & 1) * kMmaTile * ld;
-    // ---- scores of this warp's 16 keys
-    float s[2][4] = {};
-    for (int kk = 0; kk < Dk; kk += 16) {
-      uint32_t a[4];
-      const bf16* qa = Qs + g * ld + kk + 2 * t4;
-      a[0] = *reinterpret_cast<const uint32_t*>(qa);
-      a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * ld);
-      a[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * ld + 8);
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const bf16* kb = K + (size_t)(16 * warp + 8 * j + g) * ld + kk + 2 * t4;
-        uint32_t bb[2] = {*reinterpret_cast<const uint32_t*>(kb),
-                          *reinterpret_cast<const uint32_t*>(kb + 8)};
-        mma_bf16(s[j], a, bb);
-      }
+    // ---- scores of this warp's 8 keys
+    float s0[4] = {}, s1[4] = {};
+    const bf16* qa = Qs + a_row * ld + a_col;
+    const bf16* kb = K + (size_t)b_row * ld + b_col;
+    int kk = 0;
+#pragma unroll 2
+    for (; kk + 32 <= Dk; kk += 32) {
+      uint32_t a0[4], a1[4], b0[2], b1[2];
+      ldsm_x4(a0, qa + kk);
+      ldsm_x2(b0, kb + kk);
+      ldsm_x4(a1, qa + kk + 16);
+      ldsm_x2(b1, kb + kk + 16);
+      mma_bf16(s0, a0, b0);
+      mma_bf16(s1, a1, b1);
     }
-    const int key0 = lo + it * kMmaTile + 16 * warp + 2 * t4;
+    if (kk < Dk) {
+      uint32_t a0[4], b0[2];
+      ldsm_x4(a0, qa + kk);
+      ldsm_x2(b0, kb + kk);
+      mma_bf16(s0, a0, b0);
+    }
+    float s[4];
+    const int key0 = lo + it * kMmaTile + 8 * warp + 2 * t4;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = key0 + 8 * j + (e & 1);
-        s[j][e] = key <= p ? s[j][e] * scale : -INFINITY;
-        mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
-      }
+    for (int e = 0; e < 4; ++e) {
+      s[e] = key0 + (e & 1) <= p ? (s0[e] + s1[e]) * scale : -INFINITY;
+      mx[e >> 1] = fmaxf(mx[e >> 1], s[e]);
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -295,19 +319,20 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = g + 8 * r;
-      const float mt = fmaxf(fmaxf(red[row], red[16 + row]), fmaxf(red[32 + row], red[48 + row]));
+      float mt = red[row];
+#pragma unroll
+      for (int w = 1; w < kMmaWarps; ++w) mt = fmaxf(mt, red[w * 16 + row]);
       const float mn = fmaxf(m[r], mt);
       corr[r] = expf(m[r] - mn);
       m[r] = mn;
       lsum[r] *= corr[r];
     }
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const float p0 = expf(s[j][0] - m[0]), p1 = expf(s[j][1] - m[0]);
-      const float p2 = expf(s[j][2] - m[1]), p3 = expf(s[j][3] - m[1]);
+    {
+      const float p0 = expf(s[0] - m[0]), p1 = expf(s[1] - m[0]);
+      const float p2 = expf(s[2] - m[1]), p3 = expf(s[3] - m[1]);
       lsum[0] += p0 + p1;
       lsum[1] += p2 + p3;
-      const int col = 16 * warp + 8 * j + 2 * t4;
+      const int col = 8 * warp + 2 * t4;
       *reinterpret_cast<uint32_t*>(Ps + g * pld + col) = pack_bf16(p0, p1);
       *reinterpret_cast<uint32_t*>(Ps + (g + 8) * pld + col) = pack_bf16(p2, p3);
     }
@@ -317,23 +342,18 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
       o[j][2] *= corr[1], o[j][3] *= corr[1];
     }
     __syncthreads();
-    // ---- this warp's quarter of the latent channels
+    // ---- this warp's share of the latent channels
 #pragma unroll
     for (int ks = 0; ks < kMmaTile; ks += 16) {
       uint32_t a[4];
-      const bf16* pa = Ps + g * pld + ks + 2 * t4;
-      a[0] = *reinterpret_cast<const uint32_t*>(pa);
-      a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * pld);
-      a[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * pld + 8);
+      ldsm_x4(a, Ps + a_row * pld + ks + a_col);
+      const bf16* vrow = K + (size_t)(ks + (lane & 15)) * ld;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        if (j < ntw) {
-          const bf16* vb = K + (size_t)(ks + (lane & 15)) * ld + (warp * ntw + j) * 8;
+        const int ct = warp * ntw + j;
+        if (j < ntw && ct < ctiles) {
           uint32_t bb[2];
-          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
-                       : "=r"(bb[0]), "=r"(bb[1])
-                       : "r"(smem_u32(vb)));
+          ldsm_x2_trans(bb, vrow + ct * 8);
           mma_bf16(o[j], a, bb);
         }
       }
@@ -351,13 +371,18 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   for (int r = 0; r < 2; ++r) {
     const int row = g + 8 * r, h = h0 + row;
     if (h >= H) continue;
-    const float inv = 1.f / ((red[row] + red[16 + row]) + (red[32 + row] + red[48 + row]));
+    float l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) l += red[w * 16 + row];
+    const float inv = 1.f / l;
     bf16* dst = out + ((size_t)h * num_tokens + t) * C;
 #pragma unroll
-    for (int j = 0; j < NT; ++j)
-      if (j < ntw)
-        *reinterpret_cast<uint32_t*>(dst + (warp * ntw + j) * 8 + 2 * t4) =
+    for (int j = 0; j < NT; ++j) {
+      const int ct = warp * ntw + j;
+      if (j < ntw && ct < ctiles)
+        *reinterpret_cast<uint32_t*>(dst + ct * 8 + 2 * t4) =
             pack_bf16(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+    }
   }
 }
 
@@ -392,11 +417,11 @@ GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const 
   if (T <= 0) return 0;
   if (C > kLatMaxC || C <= 0 || R < 0) return -3;
   const int Dk = C + R;
-  if (dtype == GF_BF16 && C % 32 == 0 && R % 16 == 0 && (uintptr_t)c_pages % 16 == 0 &&
+  if (dtype == GF_BF16 && C % 16 == 0 && R % 16 == 0 && (uintptr_t)c_pages % 16 == 0 &&
       (uintptr_t)r_pages % 16 == 0) {
     const int ld = Dk + 8;
     const size_t bytes = ((size_t)16 * ld + (size_t)2 * kMmaTile * ld + 16 * (kMmaTile + 8)) * 2 +
-                         64 * sizeof(float);
+                         kMmaWarps * 16 * sizeof(float);
     if (bytes <= 220 * 1024) {
       static OncePerDevice once_mma;
       const int rc = once_mma.run([] {
@@ -405,22 +430,22 @@ GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const 
   if (e == cudaSuccess)                                                                     \
     e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT>,                               \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-        GF_ATTR(2) GF_ATTR(4) GF_ATTR(8) GF_ATTR(16)
+        GF_ATTR(1) GF_ATTR(2) GF_ATTR(4) GF_ATTR(8)
 #undef GF_ATTR
         return e;
       });
       if (rc) return rc;
-      const dim3 grid(T, (H + 15) / 16), block(128);
+      const dim3 grid(T, (H + 15) / 16), block(kMmaWarps * 32);
       auto st = (cudaStream_t)stream;
 #define GF_GO(NT)                                                                              \
-  if (C <= 32 * NT)                                                                            \
+  if (C <= 64 * NT)                                                                            \
     return launch_kernel(latent_attention_mma_kernel<NT>, grid, block, bytes, st, q_lat, q_rot, \
                          (const bf*)c_pages, (const bf*)r_pages, block_table, table_stride,     \
                          seq_of_token, positions, (bf*)out, T, H, C, R, page_size, window, scale)
+      GF_GO(1);
       GF_GO(2);
       GF_GO(4);
       GF_GO(8);
-      GF_GO(16);
 #undef GF_GO
     }
   }

@@ -117,19 +117,26 @@ class GatedLinear:
     gate_1, up_1, ...) so that ``x`` is read once and a gate meets its up value in neighbouring
     accumulator rows: the tcgen05 kernel combines them in its epilogue and writes only the
     product.  Gate and up are rounded to the activation dtype before they are combined, whichever
-    kernel runs, so the result does not depend on the kernel chosen."""
+    kernel runs, so the result does not depend on the kernel chosen.
 
-    def __init__(self, gate: torch.Tensor, up: torch.Tensor):
+    ``clamped = (limit, alpha, up_shift)`` replaces the activation by ``min(g, limit) *
+    sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + up_shift)``; the kernels' gated
+    epilogues take the three constants where a plain product would take its bias."""
+
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, clamped=None):
         assert gate.shape == up.shape and gate.dtype == up.dtype
         self.intermediate, k = gate.shape
         self.proj = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.intermediate, k))
+        self.clamped = None if clamped is None else tuple(float(c) for c in clamped)
+        self.act = None if clamped is None else torch.tensor(
+            self.clamped, dtype=torch.float32, device=gate.device)
 
     def __call__(self, x) -> torch.Tensor:
         if hasattr(x, "materialize"):                 # a normalisation not computed yet
             if self.proj.dtype == torch.bfloat16 and x.scaled is not None \
                     and x.scaled.shape[0] <= _gemm_bf16().MAX_TOKENS:
                 gb = _gemm_bf16()
-                z = gb.gemm(x.scaled, self.proj.weight, None, torch.bfloat16, epi=2,
+                z = gb.gemm(x.scaled, self.proj.weight, self.act, torch.bfloat16, epi=2,
                             scale=gb.RowScale(x.summed.sumsq, x.eps))
                 if z is not None:
                     return z
@@ -137,11 +144,14 @@ class GatedLinear:
         if x.dtype == torch.bfloat16:
             from . import gemm_bf16, gemm_prefill
             if x.shape[0] <= gemm_bf16.MAX_TOKENS:
-                z = gemm_bf16.gemm(x, self.proj.weight, None, torch.bfloat16, epi=2)
+                z = gemm_bf16.gemm(x, self.proj.weight, self.act, torch.bfloat16, epi=2)
                 if z is not None:
                     return z
             elif x.shape[0] >= PREFILL_GATED_MIN_TOKENS:
-                z = gemm_prefill.gemm(x, self.proj.weight, None, torch.bfloat16, epi=2)
+                z = gemm_prefill.gemm(x, self.proj.weight, self.act, torch.bfloat16, epi=2)
                 if z is not None:
                     return z
+        if self.clamped is not None:
+            from . import clamped_glu
+            return clamped_glu(self.proj(x), *self.clamped)
         return silu_mul(self.proj(x))

@@ -71,13 +71,12 @@ class ClampedGLU(FeedForward):
                 TensorSpec(self.down_key, (h, i))]
 
     def load(self, tensors, dtype, device):
-        g, u = tensors[self.gate_key], tensors[self.up_key]
-        self.gate_up = ops.Linear(torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]))
+        self.gate_up = ops.GatedLinear(tensors[self.gate_key], tensors[self.up_key],
+                                       clamped=(self.limit, self.alpha, self.up_shift))
         self.down = ops.Linear(tensors[self.down_key], None, out_dtype=torch.float32)
 
     def forward(self, x, ctx):
-        z = ops.clamped_glu(self.gate_up(x), self.limit, self.alpha, self.up_shift)
-        return self.down(z)
+        return self.down(self.gate_up(x))
 
 
 register_feed_forward("clamped_glu", ClampedGLU)

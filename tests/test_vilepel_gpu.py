@@ -358,3 +358,26 @@ def test_grouped_products_against_one_pair_at_a_time(dtype, K, F, E, top, T):
             want[t] += float(wgt[t, k]) * (z @ w2[e].double().T)
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
     assert torch.allclose(out.double(), want, atol=tol * float(want.abs().max()), rtol=tol)
+
+
+@pytest.mark.parametrize("T", [1, 8, 40, 100, 800, 1100])
+def test_clamped_gate_in_the_products_epilogues(T):
+    """The clamped sigmoid-gated activation inside the gated products (few tokens: the split-K
+    tcgen05 kernel; many: the persistent one; in between a library product and the activation
+    kernel) against the formula on the bf16-rounded gate and up values."""
+    from ginfer_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(T)
+    K, I = 192, 328
+    x = torch.randn(T, K, generator=g, device="cuda").to(torch.bfloat16)
+    wg = (torch.randn(I, K, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    wu = (torch.randn(I, K, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    lin = ops.GatedLinear(wg, wu, clamped=(1.5, 1.702, 1.0))
+    z = lin(x)
+    gate = (x.double() @ wg.double().T).to(torch.bfloat16).double()
+    up = (x.double() @ wu.double().T).to(torch.bfloat16).double()
+    want = plain.gelu_sigmoid_glu(gate, up, 1.5)
+    assert z.shape == (T, I) and z.dtype == torch.bfloat16
+    assert (gate > 1.5).any() and (up.abs() > 1.5).any()          # the clamps are at work
+    assert float((z.double() - want).abs().max()) <= 0.03 * float(want.abs().max())
+    from ginfer_b200.ops import gemm_bf16
+    gemm_bf16.check_errors("cuda:0")

@@ -10,9 +10,9 @@
 //   delta_conv_state_kernel  a thread a (request, channel): the slot's last inputs after the step.
 //   delta_recurrence_kernel  per (request, head): S <- g * S (rows); u = beta (v - S^T k);
 //                            S <- S + k u^T; o = S^T q, token after token.  The columns of S are
-//                            independent: four lanes share a column (a quarter of the rows each, in
-//                            registers), a block holds 16 or 32 columns.  The tokens' operands come
-//                            through two stages of shared memory, a chunk ahead (cp.async).
+//                            independent: four or sixteen lanes share a column (a share of the rows
+//                            each, in registers).  The tokens' operands come through two stages of
+//                            shared memory, a chunk ahead (cp.async).
 //   delta_output_kernel      a warp a (token, head): o / rms(o) * w * sigmoid(gate).
 #include "common.cuh"
 
@@ -103,7 +103,7 @@ __global__ void delta_conv_state_kernel(const T* __restrict__ proj, int ld,
   }
 }
 
-constexpr int kLanesPerColumn = 4;
+constexpr int kRecurrenceThreads = 128;
 constexpr int kMaxColumnsPerBlock = 32;
 
 __device__ __forceinline__ void copy_async_4(float* dst, const float* src) {
@@ -115,22 +115,26 @@ __device__ __forceinline__ void copy_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// A block = (request, head, `cols` columns of S); blockDim.x = 4 * cols.  The tokens' k, q, g rows
-// (padded to Dp = 4 * DPER floats, the padding zero), the block's v columns and beta come through
-// two stages of shared memory, CHUNK tokens each, asked for one chunk ahead with cp.async.
-template <int DPER, int CHUNK>
-__global__ void __launch_bounds__(kLanesPerColumn * kMaxColumnsPerBlock)
+// A block = (request, head, 128 / LP columns of S); LP lanes share a column, DPER rows each.  The
+// tokens' k, q, g rows (padded to Dp = LP * DPER floats, the padding zero), the block's v columns and
+// beta come through two stages of shared memory, CHUNK tokens each, asked for one chunk ahead with
+// cp.async.  LP = 4 where requests x heads x columns fill the device (decode batches); LP = 16
+// where they do not (one long prompt): a token is a chain of dependent instructions for a warp, and
+// with four times the lanes a column the chain is a quarter as long and four times as many warps
+// share an SM's schedulers.
+template <int DPER, int LP, int CHUNK>
+__global__ void __launch_bounds__(kRecurrenceThreads)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
                         const float* __restrict__ v, const float* __restrict__ g,
                         const float* __restrict__ beta, float* __restrict__ state,
                         const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids,
                         DeltaDims dm, float* __restrict__ o) {
-  constexpr int Dp = kLanesPerColumn * DPER;
+  constexpr int Dp = LP * DPER;
   constexpr int kTok = 3 * Dp + kMaxColumnsPerBlock + 4;      // floats a token in a stage
   extern __shared__ __align__(16) float stage[];               // [2][CHUNK][kTok]
-  const int cols = blockDim.x >> 2;
+  constexpr int cols = kRecurrenceThreads / LP;
   const int b = blockIdx.x / dm.H, h = blockIdx.x - b * dm.H;
-  const int part = threadIdx.x & (kLanesPerColumn - 1), lc = threadIdx.x >> 2;
+  const int part = threadIdx.x % LP, lc = threadIdx.x / LP;
   const int col0 = blockIdx.y * cols, col = col0 + lc;
   pdl_trigger();
   const int D = dm.D, Vd = dm.Vd;
@@ -222,8 +226,8 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
 #pragma unroll
       for (int i = 0; i < DPER; ++i) d4[i & 3] = fmaf(S[i], kc[i], d4[i & 3]);
       dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+#pragma unroll
+      for (int sh = 1; sh < LP; sh <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sh);
       const float u = bc * (vc - dot);
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -239,8 +243,8 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
         o4[3] = fmaf(S[4 * i + 3], qq.w, o4[3]);
       }
       float out = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-      out += __shfl_xor_sync(0xffffffffu, out, 1);
-      out += __shfl_xor_sync(0xffffffffu, out, 2);
+#pragma unroll
+      for (int sh = 1; sh < LP; sh <<= 1) out += __shfl_xor_sync(0xffffffffu, out, sh);
       if (part == 0 && col_ok) o[(size_t)(ta + tt) * HV + (size_t)h * Vd + col] = out;
     }
     __syncthreads();                               // the stage is free for the chunk after next
@@ -335,22 +339,26 @@ GF_EXPORT int gf_delta_recurrence(const float* qn, const float* kn, const float*
   if (H % G) return -3;
   const DeltaDims dm = dims_of(H, G, D, Vd, 1, state_stride, 0);
   auto st = (cudaStream_t)stream;
-  // few (request, head) pairs: narrower blocks, so that more SMs take part
-  const int cols = (long long)B * H * ((Vd + 31) / 32) < 148 ? 16 : 32;
+  // few (request, head, column) triples: sixteen lanes a column instead of four (see the kernel)
+  const bool wide = (long long)B * H * ((Vd + 31) / 32) < 2 * 148;
+  const int cols = kRecurrenceThreads / (wide ? 16 : 4);
   const dim3 grid(B * H, (Vd + cols - 1) / cols);
-  const dim3 block(kLanesPerColumn * cols);
-#define GF_GO(DPER, CHUNK)                                                                        \
-  if (D <= kLanesPerColumn * DPER) {                                                              \
-    const size_t smem = (size_t)2 * CHUNK * (3 * kLanesPerColumn * DPER + kMaxColumnsPerBlock + 4) * \
-                        sizeof(float);                                                            \
-    return launch_kernel(delta_recurrence_kernel<DPER, CHUNK>, grid, block, smem, st, qn, kn, v, g, \
-                         beta, state, cu_seqlens, slot_ids, dm, o);                               \
+  const dim3 block(kRecurrenceThreads);
+#define GF_GO(DPER, LP, CHUNK)                                                                     \
+  if (wide == (LP == 16) && D <= LP * DPER) {                                                      \
+    const size_t smem =                                                                            \
+        (size_t)2 * CHUNK * (3 * LP * DPER + kMaxColumnsPerBlock + 4) * sizeof(float);             \
+    return launch_kernel(delta_recurrence_kernel<DPER, LP, CHUNK>, grid, block, smem, st, qn, kn,   \
+                         v, g, beta, state, cu_seqlens, slot_ids, dm, o);                          \
   }
-  GF_GO(4, 8)
-  GF_GO(8, 8)
-  GF_GO(16, 8)
-  GF_GO(32, 8)
-  GF_GO(64, 4)
+  GF_GO(4, 4, 8)
+  GF_GO(8, 4, 8)
+  GF_GO(16, 4, 8)
+  GF_GO(32, 4, 8)
+  GF_GO(64, 4, 4)
+  GF_GO(4, 16, 8)
+  GF_GO(8, 16, 8)
+  GF_GO(16, 16, 4)
 #undef GF_GO
   return -3;
 }

@@ -169,17 +169,19 @@ __global__ void latent_attention_kernel(const float* __restrict__ q_lat,   // [H
 
 
 // ---- the same attention on the tensor cores (bf16 cache) ----------------------------------------
-// A block = one token x 16 heads (the rows of an m16n8k16 tile), eight warps.  Keys come in tiles of
-// 64 through two stages of shared memory (16-byte cp.async straight from the pages, rows past the
-// token's position zero-filled).  Scores: warp w takes keys 8 w .. 8 w + 7 of the tile over the whole
-// reduction [c | r] (two accumulators, even and odd k-steps, so that the products do not wait for
-// one another); the row maxima meet in shared memory; P goes to shared memory as bf16 and every
-// warp multiplies it with its share of the latent channels, read from the SAME tile (the values are
-// the first C channels of the keys) through transposing ldmatrix loads.  Running maximum, sums and
+// A block = one token x 16 heads (the rows of an m16n8k16 tile), sixteen warps.  Keys come in tiles
+// of 64 through two stages of shared memory (16-byte cp.async straight from the pages, rows past the
+// token's position zero-filled).  Scores: warp w takes keys 8 (w % 8) .. + 7 of the tile over one
+// half (w / 8) of the reduction [c | r] (two accumulators, even and odd k-steps, so that the
+// products do not wait for one another); the halves and then the row maxima meet in shared memory;
+// P goes to shared memory as bf16 and every warp multiplies it with its share of the latent
+// channels, read from the SAME tile (the values are the first C channels of the keys) through
+// transposing ldmatrix loads.  With one block of this size an SM (its shared memory holds the two
+// key stages) the sixteen warps are what hides the latencies of the chain.  Running maximum, sums and
 // the output accumulator are fp32; the query is rounded to bf16 once.
-// Needs C % 16 == 0, R % 16 == 0, C <= 64 * NT (NT column tiles of 8 a warp).
+// Needs C % 16 == 0, R % 16 == 0, C <= 128 * NT (NT column tiles of 8 a warp).
 constexpr int kMmaTile = 64;
-constexpr int kMmaWarps = 8;
+constexpr int kMmaWarps = 16;
 
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
   const int n = valid ? 16 : 0;
@@ -229,6 +231,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   bf16* Ks = Qs + 16 * ld;                                   // [2][64][ld]
   bf16* Ps = Ks + 2 * kMmaTile * ld;                         // [16][pld]
   float* red = reinterpret_cast<float*>(Ps + 16 * pld);      // [8][16]
+  float* sred = red + 8 * 16;                                // [2][16][64]: the halves' scores
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
   const int t = blockIdx.x, h0 = blockIdx.y * 16;
   pdl_trigger();
@@ -247,11 +250,11 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   const int nchunk = Dk >> 3;
   auto ask = [&](int tile) {
     bf16* dst = Ks + (size_t)(tile & 1) * kMmaTile * ld;
-    const int j = threadIdx.x >> 2;                          // four threads a key
+    const int j = threadIdx.x >> 3;                          // eight threads a key
     const int c = lo + tile * kMmaTile + j;
     const bool ok = c <= p;
     const size_t slot = ok ? (size_t)tbl[c / page_size] * page_size + c % page_size : 0;
-    for (int i = threadIdx.x & 3; i < nchunk; i += 4) {
+    for (int i = threadIdx.x & 7; i < nchunk; i += 8) {
       const int d = i << 3;
       const bf16* src = d < C ? c_pages + slot * C + d : r_pages + slot * R + (d - C);
       cp_async_16(dst + (size_t)j * ld + d, src, ok);
@@ -268,7 +271,10 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   // ldmatrix addresses: A (16 rows x 16 k): lanes 0-15 rows, lanes 16-31 the second 8 k;
   // B of the scores (8 keys x 16 k): lanes 0-7 keys at k, lanes 8-15 the same keys at k + 8
   const int a_row = lane & 15, a_col = (lane >> 4) << 3;
-  const int b_row = 8 * warp + (lane & 7), b_col = ((lane >> 3) & 1) << 3;
+  const int kg = warp & 7, half = warp >> 3;                 // this warp's keys and k half
+  const int b_row = 8 * kg + (lane & 7), b_col = ((lane >> 3) & 1) << 3;
+  const int k_mid = ((Dk >> 4) >> 1) << 4;                   // the first half's channels
+  const int k_lo = half ? k_mid : 0, k_hi = half ? Dk : k_mid;
   ask(0);
   for (int it = 0; it < ntiles; ++it) {
     if (it + 1 < ntiles) {
@@ -283,9 +289,9 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     float s0[4] = {}, s1[4] = {};
     const bf16* qa = Qs + a_row * ld + a_col;
     const bf16* kb = K + (size_t)b_row * ld + b_col;
-    int kk = 0;
+    int kk = k_lo;
 #pragma unroll 2
-    for (; kk + 32 <= Dk; kk += 32) {
+    for (; kk + 32 <= k_hi; kk += 32) {
       uint32_t a0[4], a1[4], b0[2], b1[2];
       ldsm_x4(a0, qa + kk);
       ldsm_x2(b0, kb + kk);
@@ -294,25 +300,39 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
       mma_bf16(s0, a0, b0);
       mma_bf16(s1, a1, b1);
     }
-    if (kk < Dk) {
+    if (kk < k_hi) {
       uint32_t a0[4], b0[2];
       ldsm_x4(a0, qa + kk);
       ldsm_x2(b0, kb + kk);
       mma_bf16(s0, a0, b0);
     }
+    {                                              // the halves meet
+      float* mine = sred + half * 16 * kMmaTile + 8 * kg + 2 * t4;
+      *reinterpret_cast<float2*>(mine + g * kMmaTile) = make_float2(s0[0] + s1[0], s0[1] + s1[1]);
+      *reinterpret_cast<float2*>(mine + (g + 8) * kMmaTile) = make_float2(s0[2] + s1[2], s0[3] + s1[3]);
+    }
+    __syncthreads();
     float s[4];
-    const int key0 = lo + it * kMmaTile + 8 * warp + 2 * t4;
+    {
+      const float* at = sred + 8 * kg + 2 * t4;
+      const float2 u0 = *reinterpret_cast<const float2*>(at + g * kMmaTile);
+      const float2 u1 = *reinterpret_cast<const float2*>(at + 16 * kMmaTile + g * kMmaTile);
+      const float2 w0 = *reinterpret_cast<const float2*>(at + (g + 8) * kMmaTile);
+      const float2 w1 = *reinterpret_cast<const float2*>(at + 16 * kMmaTile + (g + 8) * kMmaTile);
+      s[0] = u0.x + u1.x, s[1] = u0.y + u1.y, s[2] = w0.x + w1.x, s[3] = w0.y + w1.y;
+    }
+    const int key0 = lo + it * kMmaTile + 8 * kg + 2 * t4;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      s[e] = key0 + (e & 1) <= p ? (s0[e] + s1[e]) * scale : -INFINITY;
+      s[e] = key0 + (e & 1) <= p ? s[e] * scale : -INFINITY;
       mx[e >> 1] = fmaxf(mx[e >> 1], s[e]);
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      if (t4 == 0) red[warp * 16 + g + 8 * r] = mx[r];
+      if (t4 == 0 && half == 0) red[kg * 16 + g + 8 * r] = mx[r];
     }
     __syncthreads();
     float corr[2];
@@ -321,7 +341,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
       const int row = g + 8 * r;
       float mt = red[row];
 #pragma unroll
-      for (int w = 1; w < kMmaWarps; ++w) mt = fmaxf(mt, red[w * 16 + row]);
+      for (int w = 1; w < 8; ++w) mt = fmaxf(mt, red[w * 16 + row]);
       const float mn = fmaxf(m[r], mt);
       corr[r] = expf(m[r] - mn);
       m[r] = mn;
@@ -332,9 +352,11 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
       const float p2 = expf(s[2] - m[1]), p3 = expf(s[3] - m[1]);
       lsum[0] += p0 + p1;
       lsum[1] += p2 + p3;
-      const int col = 8 * warp + 2 * t4;
-      *reinterpret_cast<uint32_t*>(Ps + g * pld + col) = pack_bf16(p0, p1);
-      *reinterpret_cast<uint32_t*>(Ps + (g + 8) * pld + col) = pack_bf16(p2, p3);
+      const int col = 8 * kg + 2 * t4;
+      if (half == 0) {
+        *reinterpret_cast<uint32_t*>(Ps + g * pld + col) = pack_bf16(p0, p1);
+        *reinterpret_cast<uint32_t*>(Ps + (g + 8) * pld + col) = pack_bf16(p2, p3);
+      }
     }
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
@@ -364,7 +386,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   for (int r = 0; r < 2; ++r) {
     lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 1);
     lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 2);
-    if (t4 == 0) red[warp * 16 + g + 8 * r] = lsum[r];
+    if (t4 == 0 && half == 0) red[kg * 16 + g + 8 * r] = lsum[r];
   }
   __syncthreads();
 #pragma unroll
@@ -373,7 +395,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     if (h >= H) continue;
     float l = 0.f;
 #pragma unroll
-    for (int w = 0; w < kMmaWarps; ++w) l += red[w * 16 + row];
+    for (int w = 0; w < 8; ++w) l += red[w * 16 + row];
     const float inv = 1.f / l;
     bf16* dst = out + ((size_t)h * num_tokens + t) * C;
 #pragma unroll
@@ -421,7 +443,7 @@ GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const 
       (uintptr_t)r_pages % 16 == 0) {
     const int ld = Dk + 8;
     const size_t bytes = ((size_t)16 * ld + (size_t)2 * kMmaTile * ld + 16 * (kMmaTile + 8)) * 2 +
-                         kMmaWarps * 16 * sizeof(float);
+                         (8 * 16 + 2 * 16 * kMmaTile) * sizeof(float);
     if (bytes <= 220 * 1024) {
       static OncePerDevice once_mma;
       const int rc = once_mma.run([] {
@@ -430,7 +452,7 @@ GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const 
   if (e == cudaSuccess)                                                                     \
     e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT>,                               \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-        GF_ATTR(1) GF_ATTR(2) GF_ATTR(4) GF_ATTR(8)
+        GF_ATTR(1) GF_ATTR(2) GF_ATTR(4)
 #undef GF_ATTR
         return e;
       });
@@ -438,14 +460,13 @@ GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const 
       const dim3 grid(T, (H + 15) / 16), block(kMmaWarps * 32);
       auto st = (cudaStream_t)stream;
 #define GF_GO(NT)                                                                              \
-  if (C <= 64 * NT)                                                                            \
+  if (C <= 128 * NT)                                                                           \
     return launch_kernel(latent_attention_mma_kernel<NT>, grid, block, bytes, st, q_lat, q_rot, \
                          (const bf*)c_pages, (const bf*)r_pages, block_table, table_stride,     \
                          seq_of_token, positions, (bf*)out, T, H, C, R, page_size, window, scale)
       GF_GO(1);
       GF_GO(2);
       GF_GO(4);
-      GF_GO(8);
 #undef GF_GO
     }
   }

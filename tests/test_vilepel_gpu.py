@@ -381,3 +381,42 @@ def test_clamped_gate_in_the_products_epilogues(T):
     assert float((z.double() - want).abs().max()) <= 0.03 * float(want.abs().max())
     from ginfer_b200.ops import gemm_bf16
     gemm_bf16.check_errors("cuda:0")
+
+
+@pytest.mark.parametrize("B, H, G, D, Vd", [(40, 8, 4, 24, 36), (3, 2, 2, 130, 9), (50, 6, 1, 64, 32)])
+def test_delta_rule_batches_against_a_loop(B, H, G, D, Vd):
+    """Many requests of unequal lengths in one launch (both widths of the kernel: four lanes a
+    column where the batch fills the device, sixteen where it does not), states in shuffled
+    slots, against the recurrence written as a loop in float64."""
+    from ginfer_b200.ops import delta
+    g0 = torch.Generator().manual_seed(B)
+    lens = [1 + (7 * b) % 5 for b in range(B)]
+    T = sum(lens)
+    q = torch.randn(T, G, D, generator=g0) / D ** 0.5
+    k = torch.nn.functional.normalize(torch.randn(T, G, D, generator=g0), dim=-1)
+    v = torch.randn(T, H, Vd, generator=g0)
+    g = torch.rand(T, H, D, generator=g0) * 0.5 + 0.5
+    beta = torch.rand(T, H, generator=g0)
+    slots = torch.randperm(B + 3, generator=g0)[:B]
+    state0 = torch.randn(B + 3, H * D * Vd + 5, generator=g0)
+    state = state0.clone().cuda()
+    ctx = _Ctx()
+    ctx.num_seqs = B
+    ctx.slot_ids = slots.int().cuda()
+    cu = torch.tensor([0] + lens).cumsum(0)
+    ctx.cu_seqlens_q = cu.int().cuda()
+    o = delta.recurrence(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), state, ctx).cpu()
+    per = H // G
+    for b in range(B):
+        S = state0[slots[b], :H * D * Vd].double().reshape(H, D, Vd).clone()
+        for t in range(int(cu[b]), int(cu[b + 1])):
+            for n in range(H):
+                S[n] = g[t, n].double()[:, None] * S[n]
+                u = beta[t, n].double() * (v[t, n].double() - S[n].T @ k[t, n // per].double())
+                S[n] = S[n] + torch.outer(k[t, n // per].double(), u)
+                assert torch.allclose(o[t, n].double(), S[n].T @ q[t, n // per].double(), atol=1e-4)
+        got = state[slots[b]].cpu()
+        assert torch.allclose(got[:H * D * Vd].double(), S.reshape(-1), atol=1e-4)
+        assert torch.equal(got[H * D * Vd:], state0[slots[b], H * D * Vd:])
+    untouched = [s for s in range(B + 3) if s not in set(slots.tolist())]
+    assert torch.equal(state[untouched].cpu(), state0[untouched])

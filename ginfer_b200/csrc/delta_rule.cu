@@ -2,7 +2,7 @@
 // A request's state lives in a slot: S [heads, D, Vd] in fp32 and the last (taps - 1) inputs of the
 // short convolutions, fp32 as well.
 //
-//   delta_prepare_kernel     a block a token: causal convolution over time (taps from the rows of
+//   delta_prepare_kernel     a warp a (token, head): causal convolution over time (taps from the rows of
 //                            this step, or from the slot where the step's portion starts later than
 //                            the tap reaches) + SiLU on the q | k | v channels; q and k made unit
 //                            vectors per head (q also times D^-1/2); decay g = exp(-exp(A_log_h) *
@@ -28,6 +28,26 @@ struct DeltaDims {
   int conv_off;          // where the convolution inputs start in a slot
 };
 
+// A warp a (token, unit): units 0 .. G-1 are q heads, G .. 2G-1 k heads, then H v heads, then H
+// decay rows, then one unit for the betas.  No warp waits for another.
+template <typename T>
+__device__ __forceinline__ float conv_silu_at(const T* __restrict__ proj, int ld, int r, int i,
+                                              const float* __restrict__ cs,
+                                              const float* __restrict__ conv_w, int taps, int CH,
+                                              int ch) {
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int off = i - (taps - 1 - j);           // place of the tap's input in the portion
+    const float x = off >= 0 ? to_f32(proj[(size_t)(r - (taps - 1 - j)) * ld + ch])
+                             : cs[(size_t)(taps - 1 + off) * CH + ch];
+    acc = fmaf(conv_w[(size_t)ch * taps + j], x, acc);
+  }
+  return acc * sigmoid_f(acc);
+}
+
+constexpr int kPrepareWarps = 8;
+constexpr int kPrepareMaxPerLane = 8;              // head sizes up to 256
+
 template <typename T>
 __global__ void delta_prepare_kernel(const T* __restrict__ proj, int ld, int b_off,
                                      const float* __restrict__ a, const float* __restrict__ conv_w,
@@ -40,45 +60,51 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, int ld, int b_o
                                      float* __restrict__ qn, float* __restrict__ kn,
                                      float* __restrict__ v, float* __restrict__ g,
                                      float* __restrict__ beta) {
-  extern __shared__ float y[];                    // the token's convolved channels
   const int r = blockIdx.x;
+  const int unit = blockIdx.y * kPrepareWarps + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   pdl_trigger();
   pdl_wait();
+  const int G = dm.G, H = dm.H, D = dm.D, Vd = dm.Vd;
+  if (unit >= 2 * G + 2 * H + 1) return;
   const int b = seq_of_token[r];
   const int i = r - cu_seqlens[b];                // place in this step's portion
   const float* cs = state + (size_t)slot_ids[b] * dm.state_stride + dm.conv_off;
-  const int taps = dm.taps, CH = dm.channels;
-  for (int ch = threadIdx.x; ch < CH; ch += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {
-      const int off = i - (taps - 1 - j);         // place of the tap's input in the portion
-      const float x = off >= 0 ? to_f32(proj[(size_t)(r - (taps - 1 - j)) * ld + ch])
-                               : cs[(size_t)(taps - 1 + off) * CH + ch];
-      acc = fmaf(conv_w[(size_t)ch * taps + j], x, acc);
-    }
-    y[ch] = acc * sigmoid_f(acc);
-  }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const int GD = dm.G * dm.D;
-  for (int u = warp; u < 2 * dm.G; u += nwarps) {  // unit vectors: q heads, then k heads
-    const float* src = y + (size_t)u * dm.D;
+  const int taps = dm.taps, CH = dm.channels, GD = G * D;
+  if (unit < 2 * G) {                             // a q or k head: convolve, activate, unit vector
+    const int ch0 = unit * D;                     // q heads and k heads follow one another
+    float y[kPrepareMaxPerLane];
     float ss = 0.f;
-    for (int d = lane; d < dm.D; d += 32) ss += src[d] * src[d];
+#pragma unroll
+    for (int u = 0; u < kPrepareMaxPerLane; ++u) {
+      const int d = lane + 32 * u;
+      y[u] = d < D ? conv_silu_at(proj, ld, r, i, cs, conv_w, taps, CH, ch0 + d) : 0.f;
+      ss += y[u] * y[u];
+    }
     ss = warp_sum(ss);
-    const bool is_q = u < dm.G;
-    const float f = (is_q ? rsqrtf((float)dm.D) : 1.f) / sqrtf(ss + 1e-6f);
-    float* dst = (is_q ? qn : kn) + (size_t)r * GD + (size_t)(is_q ? u : u - dm.G) * dm.D;
-    for (int d = lane; d < dm.D; d += 32) dst[d] = src[d] * f;
+    const bool is_q = unit < G;
+    const float f = (is_q ? rsqrtf((float)D) : 1.f) / sqrtf(ss + 1e-6f);
+    float* dst = (is_q ? qn : kn) + (size_t)r * GD + (size_t)(is_q ? unit : unit - G) * D;
+#pragma unroll
+    for (int u = 0; u < kPrepareMaxPerLane; ++u) {
+      const int d = lane + 32 * u;
+      if (d < D) dst[d] = y[u] * f;
+    }
+  } else if (unit < 2 * G + H) {                  // a v head
+    const int h = unit - 2 * G;
+    for (int j = lane; j < Vd; j += 32)
+      v[((size_t)r * H + h) * Vd + j] =
+          conv_silu_at(proj, ld, r, i, cs, conv_w, taps, CH, 2 * GD + h * Vd + j);
+  } else if (unit < 2 * G + 2 * H) {              // a head's decays
+    const int h = unit - 2 * G - H;
+    const float rate = expf(A_log[h]);
+    for (int d = lane; d < D; d += 32) {
+      const size_t at = ((size_t)r * H + h) * D + d;
+      g[at] = expf(-rate * softplus_f(a[at] + dt_bias[h * D + d]));
+    }
+  } else {
+    for (int h = lane; h < H; h += 32)
+      beta[(size_t)r * H + h] = sigmoid_f(to_f32(proj[(size_t)r * ld + b_off + h]));
   }
-  const int HV = dm.H * dm.Vd, HD = dm.H * dm.D;
-  for (int j = threadIdx.x; j < HV; j += blockDim.x) v[(size_t)r * HV + j] = y[2 * GD + j];
-  for (int j = threadIdx.x; j < HD; j += blockDim.x) {
-    const float rate = expf(A_log[j / dm.D]);
-    g[(size_t)r * HD + j] = expf(-rate * softplus_f(a[(size_t)r * HD + j] + dt_bias[j]));
-  }
-  for (int h = threadIdx.x; h < dm.H; h += blockDim.x)
-    beta[(size_t)r * dm.H + h] = sigmoid_f(to_f32(proj[(size_t)r * ld + b_off + h]));
 }
 
 template <typename T>
@@ -208,44 +234,58 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
     __syncthreads();
     const float* st = stage + (size_t)(c & 1) * CHUNK * kTok;
     const int ta = t0 + c * CHUNK, n = min(CHUNK, t1 - ta);
-    for (int tt = 0; tt < n; ++tt) {
-      const float* tok = st + (size_t)tt * kTok;
-      const float4* k4 = reinterpret_cast<const float4*>(tok + row0);
-      const float4* q4 = reinterpret_cast<const float4*>(tok + Dp + row0);
-      const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * Dp + row0);
-      const float vc = tok[3 * Dp + lc], bc = tok[3 * Dp + kMaxColumnsPerBlock];
-      float kc[DPER];
-      float dot = 0.f;
+    // The chunk's tokens, unrolled: the read-out o = S^T q of a token is off the chain that the
+    // next token waits for (only u is on it), so its lane reduction is left until the chunk is
+    // done and the eight reductions run side by side.
+    float outp[CHUNK];
 #pragma unroll
-      for (int i = 0; i < DPER / 4; ++i) {
-        const float4 kk = k4[i], gg = g4[i];
-        kc[4 * i] = kk.x, kc[4 * i + 1] = kk.y, kc[4 * i + 2] = kk.z, kc[4 * i + 3] = kk.w;
-        S[4 * i] *= gg.x, S[4 * i + 1] *= gg.y, S[4 * i + 2] *= gg.z, S[4 * i + 3] *= gg.w;
+    for (int tt = 0; tt < CHUNK; ++tt) {
+      outp[tt] = 0.f;
+      if (tt < n) {
+        const float* tok = st + (size_t)tt * kTok;
+        const float4* k4 = reinterpret_cast<const float4*>(tok + row0);
+        const float4* q4 = reinterpret_cast<const float4*>(tok + Dp + row0);
+        const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * Dp + row0);
+        const float vc = tok[3 * Dp + lc], bc = tok[3 * Dp + kMaxColumnsPerBlock];
+        float kc[DPER];
+#pragma unroll
+        for (int i = 0; i < DPER / 4; ++i) {
+          const float4 kk = k4[i], gg = g4[i];
+          kc[4 * i] = kk.x, kc[4 * i + 1] = kk.y, kc[4 * i + 2] = kk.z, kc[4 * i + 3] = kk.w;
+          S[4 * i] *= gg.x, S[4 * i + 1] *= gg.y, S[4 * i + 2] *= gg.z, S[4 * i + 3] *= gg.w;
+        }
+        float d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < DPER; ++i) d4[i & 3] = fmaf(S[i], kc[i], d4[i & 3]);
+        float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+#pragma unroll
+        for (int sh = 1; sh < LP; sh <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sh);
+        const float u = bc * (vc - dot);
+        float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < DPER / 4; ++i) {
+          const float4 qq = q4[i];
+          S[4 * i] = fmaf(kc[4 * i], u, S[4 * i]);
+          S[4 * i + 1] = fmaf(kc[4 * i + 1], u, S[4 * i + 1]);
+          S[4 * i + 2] = fmaf(kc[4 * i + 2], u, S[4 * i + 2]);
+          S[4 * i + 3] = fmaf(kc[4 * i + 3], u, S[4 * i + 3]);
+          o4[0] = fmaf(S[4 * i], qq.x, o4[0]);
+          o4[1] = fmaf(S[4 * i + 1], qq.y, o4[1]);
+          o4[2] = fmaf(S[4 * i + 2], qq.z, o4[2]);
+          o4[3] = fmaf(S[4 * i + 3], qq.w, o4[3]);
+        }
+        outp[tt] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
       }
-      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+    }
 #pragma unroll
-      for (int i = 0; i < DPER; ++i) d4[i & 3] = fmaf(S[i], kc[i], d4[i & 3]);
-      dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+    for (int sh = 1; sh < LP; sh <<= 1) {
 #pragma unroll
-      for (int sh = 1; sh < LP; sh <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sh);
-      const float u = bc * (vc - dot);
-      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int tt = 0; tt < CHUNK; ++tt) outp[tt] += __shfl_xor_sync(0xffffffffu, outp[tt], sh);
+    }
+    if (part == 0 && col_ok) {
 #pragma unroll
-      for (int i = 0; i < DPER / 4; ++i) {
-        const float4 qq = q4[i];
-        S[4 * i] = fmaf(kc[4 * i], u, S[4 * i]);
-        S[4 * i + 1] = fmaf(kc[4 * i + 1], u, S[4 * i + 1]);
-        S[4 * i + 2] = fmaf(kc[4 * i + 2], u, S[4 * i + 2]);
-        S[4 * i + 3] = fmaf(kc[4 * i + 3], u, S[4 * i + 3]);
-        o4[0] = fmaf(S[4 * i], qq.x, o4[0]);
-        o4[1] = fmaf(S[4 * i + 1], qq.y, o4[1]);
-        o4[2] = fmaf(S[4 * i + 2], qq.z, o4[2]);
-        o4[3] = fmaf(S[4 * i + 3], qq.w, o4[3]);
-      }
-      float out = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-#pragma unroll
-      for (int sh = 1; sh < LP; sh <<= 1) out += __shfl_xor_sync(0xffffffffu, out, sh);
-      if (part == 0 && col_ok) o[(size_t)(ta + tt) * HV + (size_t)h * Vd + col] = out;
+      for (int tt = 0; tt < CHUNK; ++tt)
+        if (tt < n) o[(size_t)(ta + tt) * HV + (size_t)h * Vd + col] = outp[tt];
     }
     __syncthreads();                               // the stage is free for the chunk after next
   }
@@ -301,27 +341,19 @@ GF_EXPORT int gf_delta_prepare(const void* proj, int ld, int b_off, const float*
   if (T <= 0) return 0;
   if (H % G || taps < 1) return -3;
   const DeltaDims dm = dims_of(H, G, D, Vd, taps, state_stride, conv_off);
-  const size_t smem = (size_t)dm.channels * sizeof(float);
-  if (smem > 160 * 1024) return -3;
+  if (D > 32 * kPrepareMaxPerLane) return -3;
   auto st = (cudaStream_t)stream;
-  static OncePerDevice once;
-  int rc = once.run([] {
-    cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel<float>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(delta_prepare_kernel<bf>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-  });
-  if (rc) return rc;
+  const int units = 2 * G + 2 * H + 1;
+  const dim3 pgrid(T, (units + kPrepareWarps - 1) / kPrepareWarps), pblock(kPrepareWarps * 32);
+  int rc;
   if (dtype == GF_F32)
-    rc = launch_kernel(delta_prepare_kernel<float>, dim3(T), dim3(256), smem, st,
-                       (const float*)proj, ld, b_off, a, conv_w, dt_bias, A_log,
-                       (const float*)state, seq_of_token, cu_seqlens, slot_ids, dm, qn, kn, v, g,
-                       beta);
-  else
-    rc = launch_kernel(delta_prepare_kernel<bf>, dim3(T), dim3(256), smem, st, (const bf*)proj, ld,
+    rc = launch_kernel(delta_prepare_kernel<float>, pgrid, pblock, 0, st, (const float*)proj, ld,
                        b_off, a, conv_w, dt_bias, A_log, (const float*)state, seq_of_token,
                        cu_seqlens, slot_ids, dm, qn, kn, v, g, beta);
+  else
+    rc = launch_kernel(delta_prepare_kernel<bf>, pgrid, pblock, 0, st, (const bf*)proj, ld, b_off,
+                       a, conv_w, dt_bias, A_log, (const float*)state, seq_of_token, cu_seqlens,
+                       slot_ids, dm, qn, kn, v, g, beta);
   if (rc || taps == 1) return rc;
   const dim3 grid((dm.channels + 127) / 128, B);
   if (dtype == GF_F32)

@@ -248,16 +248,22 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     Qs[r * ld + d] = __float2bfloat16_rn(v);
   }
   const int nchunk = Dk >> 3;
-  auto ask = [&](int tile) {
+  // The page of this thread's key in a tile is looked up a tile ahead of the copies that need it,
+  // so that no tile waits for the table.
+  const int kj = threadIdx.x >> 3;                           // eight threads a key
+  auto page_of = [&](int tile) {
+    const int c = lo + tile * kMmaTile + kj;
+    return c <= p ? tbl[c / page_size] : -1;
+  };
+  auto ask = [&](int tile, int page) {
     bf16* dst = Ks + (size_t)(tile & 1) * kMmaTile * ld;
-    const int j = threadIdx.x >> 3;                          // eight threads a key
-    const int c = lo + tile * kMmaTile + j;
-    const bool ok = c <= p;
-    const size_t slot = ok ? (size_t)tbl[c / page_size] * page_size + c % page_size : 0;
+    const int c = lo + tile * kMmaTile + kj;
+    const bool ok = page >= 0;
+    const size_t slot = ok ? (size_t)page * page_size + c % page_size : 0;
     for (int i = threadIdx.x & 7; i < nchunk; i += 8) {
       const int d = i << 3;
       const bf16* src = d < C ? c_pages + slot * C + d : r_pages + slot * R + (d - C);
-      cp_async_16(dst + (size_t)j * ld + d, src, ok);
+      cp_async_16(dst + (size_t)kj * ld + d, src, ok);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -275,10 +281,12 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   const int b_row = 8 * kg + (lane & 7), b_col = ((lane >> 3) & 1) << 3;
   const int k_mid = ((Dk >> 4) >> 1) << 4;                   // the first half's channels
   const int k_lo = half ? k_mid : 0, k_hi = half ? Dk : k_mid;
-  ask(0);
+  ask(0, page_of(0));
+  int page_next = ntiles > 1 ? page_of(1) : -1;
   for (int it = 0; it < ntiles; ++it) {
     if (it + 1 < ntiles) {
-      ask(it + 1);
+      ask(it + 1, page_next);
+      page_next = it + 2 < ntiles ? page_of(it + 2) : -1;
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");

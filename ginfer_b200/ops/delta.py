@@ -38,8 +38,8 @@ def prepare(proj: torch.Tensor, b_off: int, a: torch.Tensor, conv_w: torch.Tenso
            ctx.num_seqs, H, G, D, Vd, taps, state.stride(0), int(conv_off), _p(qn), _p(kn), _p(v),
            _p(g), _p(beta), _code(proj.dtype), _stream())
     if rc == -3:
-        raise ValueError("the delta-rule kernels need heads to be a multiple of kv heads and the "
-                         f"convolved channels to fit shared memory; got {H}, {G}, {ch} channels")
+        raise ValueError("the delta-rule kernels need heads to be a multiple of kv heads and key "
+                         f"sizes up to 256; got {H} heads, {G} kv heads, key size {D}")
     _ok(rc, "delta_prepare")
     return qn, kn, v, g, beta
 

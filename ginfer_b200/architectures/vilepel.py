@@ -25,7 +25,8 @@ def _mixer(cfg: VilepelConfig, kind: str, m) -> PartSpec:
     if kind == "latent_attention":
         return PartSpec("latent_attention", dict(
             hidden_size=cfg.width, num_heads=m["heads"], nope_dim=m["dim"], rope_dim=m["rot_dim"],
-            v_dim=m["vdim"], kv_rank=m["kv_rank"], scale=m["scale"], window=m["mask"]["size"],
+            v_dim=m["vdim"], kv_rank=m["kv_rank"], scale=m["scale"],
+            window=m["mask"]["size"] if m.get("mask") is not None else 0,
             rotary_dims=m["rot"]["dims"], rotary_base=m["rot"]["base"], latent_eps=cfg.norm_eps,
             prefix="mix"))
     # the inner sizes of the two low-rank projections are the tensors' own; a configuration may

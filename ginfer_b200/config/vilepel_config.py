@@ -14,7 +14,7 @@ from typing import Any, Mapping
 from .model_config import ConfigError
 
 MIXER_KEYS = {
-    "latent_attention": ("heads", "dim", "rot_dim", "vdim", "kv_rank", "scale", "mask", "rot"),
+    "latent_attention": ("heads", "dim", "rot_dim", "vdim", "kv_rank", "scale", "rot"),
     "channel_delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
 }
 
@@ -139,7 +139,8 @@ class VilepelConfig:
                                       "channels; it must be an even number of them")
                 if not (float(_need(m["rot"], "base", f"layers[{i}].mixer.rot")) > 0):
                     raise ConfigError(f"config.json: layers[{i}].mixer.rot.base must be > 0")
-                _positive_int(_need(m["mask"], "size", f"layers[{i}].mixer.mask"), "mask.size")
+                if m.get("mask") is not None:          # no mask: every earlier token is seen
+                    _positive_int(_need(m["mask"], "size", f"layers[{i}].mixer.mask"), "mask.size")
             else:
                 _positive_int(m["kv_heads"], f"layers[{i}].mixer.kv_heads")
                 _positive_int(m["conv"], f"layers[{i}].mixer.conv")

@@ -19,7 +19,7 @@ namespace gf {
 
 constexpr int kLatWarps = 8;        // heads per block
 constexpr int kLatTile = 32;        // keys per tile (a lane a key)
-constexpr int kLatMaxC = 512;       // latent channels a lane can accumulate (16 registers)
+constexpr int kLatMaxC = 1024;      // latent channels a lane can accumulate (32 registers)
 
 template <typename T>
 __global__ void latent_prepare_kernel(const T* __restrict__ qd, int ld, int H, int D, int R, int C,

@@ -51,7 +51,7 @@ def attention(q_lat: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor,
            block_table.stride(0), _p(ctx.seq_of_token), _p(ctx.positions), _p(out), T, H, C, R,
            int(page_size), int(window), float(scale), _code(c_pages.dtype), _stream())
     if rc == -3:
-        raise ValueError(f"latent attention takes latent vectors of up to 512 channels whose key "
+        raise ValueError(f"latent attention takes latent vectors of up to 1024 channels whose key "
                          f"tile fits shared memory; got kv_rank={C}, rot_dim={R}")
     _ok(rc, "latent_attention")
     return out

@@ -420,3 +420,37 @@ def test_delta_rule_batches_against_a_loop(B, H, G, D, Vd):
         assert torch.equal(got[H * D * Vd:], state0[slots[b], H * D * Vd:])
     untouched = [s for s in range(B + 3) if s not in set(slots.tolist())]
     assert torch.equal(state[untouched].cpu(), state0[untouched])
+
+
+@pytest.mark.parametrize("H, C, R, keys, window, page", [
+    (16, 512, 64, 300, 150, 16), (20, 256, 32, 130, 0, 8), (5, 64, 16, 70, 33, 16),
+    (3, 48, 16, 64, 64, 16)])
+def test_latent_attention_on_tensor_cores_agrees_with_plain_arithmetic(H, C, R, keys, window, page):
+    """The tensor-core kernel (bf16 cache) against the plain fp32 one on the same values, at the
+    sizes of large layers, with more heads than a row tile and with channel counts that leave
+    warps idle; every row of a prompt, so that tiles end at every place."""
+    from ginfer_b200.ops import latent
+    g0 = torch.Generator().manual_seed(C + keys)
+    npages = -(-keys // page)
+    order = torch.randperm(npages + 2, generator=g0)[:npages]
+    c = (torch.randn(keys, C, generator=g0)).to(torch.bfloat16)
+    r = (torch.randn(keys, R, generator=g0)).to(torch.bfloat16)
+    c_pages = torch.zeros(npages + 2, page, 1, C, dtype=torch.bfloat16)
+    r_pages = torch.zeros(npages + 2, page, 1, R, dtype=torch.bfloat16)
+    for j in range(keys):
+        c_pages[order[j // page], j % page, 0] = c[j]
+        r_pages[order[j // page], j % page, 0] = r[j]
+    table = order.int().cuda()[None, :]
+    ctx = _Ctx()
+    ctx.seq_of_token = torch.zeros(keys, dtype=torch.int32, device="cuda")
+    ctx.positions = torch.arange(keys, dtype=torch.int32, device="cuda")
+    q_lat = (torch.randn(H, keys, C, generator=g0) * 0.3).to(torch.bfloat16).float().cuda()
+    q_rot = (torch.randn(keys, H, R, generator=g0) * 0.3).to(torch.bfloat16).float().cuda()
+    scale = (C + R) ** -0.5 * 3.0
+    fast = latent.attention(q_lat, q_rot, c_pages.cuda(), r_pages.cuda(), table, ctx, window, scale,
+                            page)
+    slow = latent.attention(q_lat, q_rot, c_pages.float().cuda(), r_pages.float().cuda(), table,
+                            ctx, window, scale, page)
+    assert fast.dtype == torch.bfloat16 and slow.dtype == torch.float32
+    err = (fast.float() - slow).abs().max()
+    assert float(err) <= 0.02 * float(slow.abs().max()), float(err)

@@ -179,7 +179,9 @@ __global__ void latent_attention_kernel(const float* __restrict__ q_lat,   // [H
 // transposing ldmatrix loads.  With one block of this size an SM (its shared memory holds the two
 // key stages) the sixteen warps are what hides the latencies of the chain.  Running maximum, sums and
 // the output accumulator are fp32; the query is rounded to bf16 once.
-// Needs C % 16 == 0, R % 16 == 0, C <= 128 * NT (NT column tiles of 8 a warp).
+// Needs C % 16 == 0, R % 16 == 0, C <= 128 * NT (NT column tiles of 8 a warp).  Few tokens with many
+// keys (decode steps of small batches): several blocks share a token's tiles (blockIdx.z) and a
+// second kernel merges their sums, as the decode kernel of the grouped-query attention does.
 constexpr int kMmaTile = 64;
 constexpr int kMmaWarps = 16;
 
@@ -223,7 +225,8 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
                             const int* __restrict__ seq_of_token,
                             const int* __restrict__ positions, bf16* __restrict__ out,
                             int num_tokens, int H, int C, int R, int page_size, int window,
-                            float scale) {
+                            float scale, int nsplit, float* __restrict__ part_o,
+                            float* __restrict__ part_ml) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int Dk = C + R, ld = Dk + 8;
   constexpr int pld = kMmaTile + 8;
@@ -267,7 +270,12 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  const int ntiles = (p - lo) / kMmaTile + 1;
+  // nsplit > 1 (few tokens with many keys): block z of a token takes a share of its tiles and
+  // leaves its unnormalised sums, which latent_merge_kernel puts together
+  const int all_tiles = (p - lo) / kMmaTile + 1;
+  const int share = (all_tiles + nsplit - 1) / nsplit;
+  const int tile0 = (int)blockIdx.z * share;
+  const int ntiles = min(all_tiles, tile0 + share);
   const int ctiles = C >> 3;                                 // column tiles of 8 in all
   const int ntw = (ctiles + kMmaWarps - 1) / kMmaWarps;      // of which this warp owns up to ntw
   float o[NT][4];
@@ -281,9 +289,9 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   const int b_row = 8 * kg + (lane & 7), b_col = ((lane >> 3) & 1) << 3;
   const int k_mid = ((Dk >> 4) >> 1) << 4;                   // the first half's channels
   const int k_lo = half ? k_mid : 0, k_hi = half ? Dk : k_mid;
-  ask(0, page_of(0));
-  int page_next = ntiles > 1 ? page_of(1) : -1;
-  for (int it = 0; it < ntiles; ++it) {
+  if (tile0 < ntiles) ask(tile0, page_of(tile0));
+  int page_next = tile0 + 1 < ntiles ? page_of(tile0 + 1) : -1;
+  for (int it = tile0; it < ntiles; ++it) {
     if (it + 1 < ntiles) {
       ask(it + 1, page_next);
       page_next = it + 2 < ntiles ? page_of(it + 2) : -1;
@@ -404,6 +412,18 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     float l = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) l += red[w * 16 + row];
+    if (nsplit > 1) {
+      const size_t at = ((size_t)blockIdx.z * num_tokens + t) * H + h;
+      if (warp == 0 && t4 == 0) part_ml[2 * at] = m[r], part_ml[2 * at + 1] = l;
+      float* dst = part_o + at * C;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int ct = warp * ntw + j;
+        if (j < ntw && ct < ctiles)
+          *reinterpret_cast<float2*>(dst + ct * 8 + 2 * t4) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+      }
+      continue;
+    }
     const float inv = 1.f / l;
     bf16* dst = out + ((size_t)h * num_tokens + t) * C;
 #pragma unroll
@@ -413,6 +433,35 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
         *reinterpret_cast<uint32_t*>(dst + ct * 8 + 2 * t4) =
             pack_bf16(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
     }
+  }
+}
+
+// out[h, t, :] = sum_z o_z exp(m_z - M) / sum_z l_z exp(m_z - M): a warp a (token, head).
+__global__ void latent_merge_kernel(const float* __restrict__ part_o,
+                                    const float* __restrict__ part_ml, bf16* __restrict__ out,
+                                    int num_tokens, int H, int C, int nsplit) {
+  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();
+  if (pair >= num_tokens * H) return;
+  const int t = pair / H, h = pair - t * H;
+  float M = -INFINITY;
+  for (int z = 0; z < nsplit; ++z)
+    M = fmaxf(M, part_ml[2 * (((size_t)z * num_tokens + t) * H + h)]);
+  float L = 0.f;
+  for (int z = 0; z < nsplit; ++z) {
+    const size_t at = ((size_t)z * num_tokens + t) * H + h;
+    L += part_ml[2 * at + 1] * expf(part_ml[2 * at] - M);
+  }
+  bf16* dst = out + ((size_t)h * num_tokens + t) * C;
+  for (int c = lane; c < C; c += 32) {
+    float acc = 0.f;
+    for (int z = 0; z < nsplit; ++z) {
+      const size_t at = ((size_t)z * num_tokens + t) * H + h;
+      const float lz = part_ml[2 * at + 1];
+      if (lz > 0.f) acc += part_o[at * C + c] * expf(part_ml[2 * at] - M);
+    }
+    dst[c] = __float2bfloat16_rn(acc / L);
   }
 }
 
@@ -443,7 +492,8 @@ GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const 
                                   const void* r_pages, const int* block_table, int table_stride,
                                   const int* seq_of_token, const int* positions, void* out, int T,
                                   int H, int C, int R, int page_size, int window, float scale,
-                                  int dtype, void* stream) {
+                                  int dtype, int nsplit, float* part_o, float* part_ml,
+                                  void* stream) {
   if (T <= 0) return 0;
   if (C > kLatMaxC || C <= 0 || R < 0) return -3;
   const int Dk = C + R;
@@ -465,17 +515,23 @@ GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const 
         return e;
       });
       if (rc) return rc;
-      const dim3 grid(T, (H + 15) / 16), block(kMmaWarps * 32);
+      if (nsplit < 1 || (nsplit > 1 && (!part_o || !part_ml))) nsplit = 1;
+      const dim3 grid(T, (H + 15) / 16, nsplit), block(kMmaWarps * 32);
       auto st = (cudaStream_t)stream;
+      int rc2 = -3;
 #define GF_GO(NT)                                                                              \
-  if (C <= 128 * NT)                                                                           \
-    return launch_kernel(latent_attention_mma_kernel<NT>, grid, block, bytes, st, q_lat, q_rot, \
-                         (const bf*)c_pages, (const bf*)r_pages, block_table, table_stride,     \
-                         seq_of_token, positions, (bf*)out, T, H, C, R, page_size, window, scale)
+  if (rc2 == -3 && C <= 128 * NT)                                                              \
+    rc2 = launch_kernel(latent_attention_mma_kernel<NT>, grid, block, bytes, st, q_lat, q_rot,  \
+                        (const bf*)c_pages, (const bf*)r_pages, block_table, table_stride,      \
+                        seq_of_token, positions, (bf*)out, T, H, C, R, page_size, window, scale, \
+                        nsplit, part_o, part_ml)
       GF_GO(1);
       GF_GO(2);
       GF_GO(4);
 #undef GF_GO
+      if (rc2 || nsplit == 1) return rc2;
+      return launch_kernel(latent_merge_kernel, dim3((T * H + 3) / 4), dim3(128), 0, st,
+                           (const float*)part_o, (const float*)part_ml, (bf*)out, T, H, C, nsplit);
     }
   }
   const size_t smem = ((size_t)kLatTile * (Dk + 1) + (size_t)kLatWarps * Dk) * sizeof(float);

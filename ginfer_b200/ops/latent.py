@@ -33,23 +33,48 @@ def prepare(qd: torch.Tensor, H: int, D: int, R: int, C: int, rot: int, freq: to
     return q_rot
 
 
+KEY_TILE = 64           # keys a tile of the tensor-core kernel
+MAX_SPLITS = 8
+MIN_TILES_A_SPLIT = 4   # a share shorter than this costs more in the merge than it saves
+
+
+def key_splits(num_tokens: int, num_heads: int, max_keys: int, sms: int = 148) -> int:
+    """How many blocks share the keys of a token: one unless the step's blocks would leave most
+    SMs idle and a token has several tiles of keys."""
+    blocks = num_tokens * -(-num_heads // 16)
+    tiles = -(-max(1, max_keys) // KEY_TILE)
+    if blocks * 2 > sms or tiles < 2 * MIN_TILES_A_SPLIT:
+        return 1
+    return max(1, min(tiles // MIN_TILES_A_SPLIT, sms // blocks, MAX_SPLITS))
+
+
 def attention(q_lat: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor,
               r_pages: torch.Tensor, block_table: torch.Tensor, ctx, window: int, scale: float,
               page_size: int) -> torch.Tensor:
     """``q_lat [H, T, C]`` and ``q_rot [T, H, R]`` in fp32 against the cache; returns the
-    softmax-weighted latent vectors ``[H, T, C]`` in the cache's dtype."""
+    softmax-weighted latent vectors ``[H, T, C]`` in the cache's dtype.  ``ctx.max_kv_len`` (if
+    there) bounds the keys of a token and decides whether several blocks share them."""
     _cuda(q_lat, q_rot, c_pages, r_pages, block_table)
     H, T, C = q_lat.shape
     R = q_rot.shape[2]
     assert q_lat.dtype == torch.float32 and q_lat.is_contiguous()
     assert q_rot.dtype == torch.float32 and q_rot.is_contiguous() and q_rot.shape[:2] == (T, H)
     out = torch.empty((H, T, C), dtype=c_pages.dtype, device=q_lat.device)
+    nsplit, part_o, part_ml = 1, None, None
+    max_keys = int(getattr(ctx, "max_kv_len", 0) or 0)
+    if c_pages.dtype == torch.bfloat16 and max_keys > 0:
+        nsplit = key_splits(T, H, min(max_keys, window) if window > 0 else max_keys)
+        if nsplit > 1:
+            part_o = torch.empty((nsplit, T, H, C), dtype=torch.float32, device=q_lat.device)
+            part_ml = torch.empty((nsplit, T, H, 2), dtype=torch.float32, device=q_lat.device)
     f = _fn("latent_attention", "gf_latent_attention",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+             c_void_p, c_void_p], kernels=2 if nsplit > 1 else 1)
     rc = f(_p(q_lat), _p(q_rot), _p(c_pages), _p(r_pages), _p(block_table),
            block_table.stride(0), _p(ctx.seq_of_token), _p(ctx.positions), _p(out), T, H, C, R,
-           int(page_size), int(window), float(scale), _code(c_pages.dtype), _stream())
+           int(page_size), int(window), float(scale), _code(c_pages.dtype), nsplit, _p(part_o),
+           _p(part_ml), _stream())
     if rc == -3:
         raise ValueError(f"latent attention takes latent vectors of up to 1024 channels whose key "
                          f"tile fits shared memory; got kv_rank={C}, rot_dim={R}")

@@ -454,3 +454,26 @@ def test_latent_attention_on_tensor_cores_agrees_with_plain_arithmetic(H, C, R, 
     assert fast.dtype == torch.bfloat16 and slow.dtype == torch.float32
     err = (fast.float() - slow).abs().max()
     assert float(err) <= 0.02 * float(slow.abs().max()), float(err)
+
+
+@pytest.mark.parametrize("window", [0, 700, 520])
+def test_latent_attention_shares_a_tokens_keys_among_blocks_in_small_steps(window):
+    """A step of three single tokens at 798-800 keys: several blocks take a share of each token's
+    key tiles and a second kernel merges them; against the plain kernel."""
+    from ginfer_b200.ops import latent
+    H, C, R, keys, page = 16, 256, 32, 800, 16
+    g0 = torch.Generator().manual_seed(window)
+    c_pages = torch.randn(keys // page + 1, page, 1, C, generator=g0).to(torch.bfloat16).cuda()
+    r_pages = torch.randn(keys // page + 1, page, 1, R, generator=g0).to(torch.bfloat16).cuda()
+    table = torch.arange(keys // page + 1, dtype=torch.int32, device="cuda").repeat(3, 1)
+    ctx = _Ctx()
+    ctx.seq_of_token = torch.arange(3, dtype=torch.int32, device="cuda")
+    ctx.positions = torch.tensor([797, 798, 799], dtype=torch.int32, device="cuda")
+    ctx.max_kv_len = keys
+    assert latent.key_splits(3, H, min(keys, window) if window else keys) > 1
+    q_lat = (torch.randn(H, 3, C, generator=g0) * 0.3).cuda()
+    q_rot = (torch.randn(3, H, R, generator=g0) * 0.3).cuda()
+    fast = latent.attention(q_lat, q_rot, c_pages, r_pages, table, ctx, window, 0.2, page)
+    slow = latent.attention(q_lat, q_rot, c_pages.float(), r_pages.float(), table, ctx, window,
+                            0.2, page)
+    assert float((fast.float() - slow).abs().max()) <= 0.02 * float(slow.abs().max())

@@ -10,7 +10,7 @@
 //   delta_conv_state_kernel  a thread a (request, channel): the slot's last inputs after the step.
 //   delta_recurrence_kernel  per (request, head): S <- g * S (rows); u = beta (v - S^T k);
 //                            S <- S + k u^T; o = S^T q, token after token.  The columns of S are
-//                            independent: four or sixteen lanes share a column (a share of the rows
+//                            independent: four lanes or a warp share a column (a share of the rows
 //                            each, in registers).  The tokens' operands come through two stages of
 //                            shared memory, a chunk ahead (cp.async).
 //   delta_output_kernel      a warp a (token, head): o / rms(o) * w * sigmoid(gate).
@@ -144,12 +144,12 @@ __device__ __forceinline__ void copy_async_wait() {
 // A block = (request, head, 128 / LP columns of S); LP lanes share a column, DPER rows each.  The
 // tokens' k, q, g rows (padded to Dp = LP * DPER floats, the padding zero), the block's v columns and
 // beta come through two stages of shared memory, CHUNK tokens each, asked for one chunk ahead with
-// cp.async.  LP = 4 where requests x heads x columns fill the device (decode batches); LP = 16
-// where they do not (one long prompt): a token is a chain of dependent instructions for a warp, and
-// with four times the lanes a column the chain is a quarter as long and four times as many warps
-// share an SM's schedulers.
-template <int DPER, int LP, int CHUNK>
-__global__ void __launch_bounds__(kRecurrenceThreads)
+// cp.async.  LP = 4 where requests x heads x columns fill the device (decode batches); LP = 32
+// (a warp a column, eight columns a block) where they do not (one long prompt): a token is a chain
+// of dependent instructions for a warp, and with eight times the lanes a column the chain is short
+// and eight times as many warps share an SM's schedulers.
+template <int DPER, int LP, int CHUNK, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
                         const float* __restrict__ v, const float* __restrict__ g,
                         const float* __restrict__ beta, float* __restrict__ state,
@@ -158,7 +158,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   constexpr int Dp = LP * DPER;
   constexpr int kTok = 3 * Dp + kMaxColumnsPerBlock + 4;      // floats a token in a stage
   extern __shared__ __align__(16) float stage[];               // [2][CHUNK][kTok]
-  constexpr int cols = kRecurrenceThreads / LP;
+  constexpr int cols = THREADS / LP;
   const int b = blockIdx.x / dm.H, h = blockIdx.x - b * dm.H;
   const int part = threadIdx.x % LP, lc = threadIdx.x / LP;
   const int col0 = blockIdx.y * cols, col = col0 + lc;
@@ -371,26 +371,26 @@ GF_EXPORT int gf_delta_recurrence(const float* qn, const float* kn, const float*
   if (H % G) return -3;
   const DeltaDims dm = dims_of(H, G, D, Vd, 1, state_stride, 0);
   auto st = (cudaStream_t)stream;
-  // few (request, head, column) triples: sixteen lanes a column instead of four (see the kernel)
+  // few (request, head, column) triples: a warp a column instead of four lanes (see the kernel)
   const bool wide = (long long)B * H * ((Vd + 31) / 32) < 2 * 148;
-  const int cols = kRecurrenceThreads / (wide ? 16 : 4);
+  const int threads = wide ? 256 : kRecurrenceThreads;
+  const int cols = threads / (wide ? 32 : 4);
   const dim3 grid(B * H, (Vd + cols - 1) / cols);
-  const dim3 block(kRecurrenceThreads);
-#define GF_GO(DPER, LP, CHUNK)                                                                     \
-  if (wide == (LP == 16) && D <= LP * DPER) {                                                      \
+  const dim3 block(threads);
+#define GF_GO(DPER, LP, CHUNK, THREADS)                                                            \
+  if (wide == (LP == 32) && D <= LP * DPER) {                                                      \
     const size_t smem =                                                                            \
         (size_t)2 * CHUNK * (3 * LP * DPER + kMaxColumnsPerBlock + 4) * sizeof(float);             \
-    return launch_kernel(delta_recurrence_kernel<DPER, LP, CHUNK>, grid, block, smem, st, qn, kn,   \
-                         v, g, beta, state, cu_seqlens, slot_ids, dm, o);                          \
+    return launch_kernel(delta_recurrence_kernel<DPER, LP, CHUNK, THREADS>, grid, block, smem, st,  \
+                         qn, kn, v, g, beta, state, cu_seqlens, slot_ids, dm, o);                  \
   }
-  GF_GO(4, 4, 8)
-  GF_GO(8, 4, 8)
-  GF_GO(16, 4, 8)
-  GF_GO(32, 4, 8)
-  GF_GO(64, 4, 4)
-  GF_GO(4, 16, 8)
-  GF_GO(8, 16, 8)
-  GF_GO(16, 16, 4)
+  GF_GO(4, 4, 8, kRecurrenceThreads)
+  GF_GO(8, 4, 8, kRecurrenceThreads)
+  GF_GO(16, 4, 8, kRecurrenceThreads)
+  GF_GO(32, 4, 8, kRecurrenceThreads)
+  GF_GO(64, 4, 4, kRecurrenceThreads)
+  GF_GO(4, 32, 8, 256)
+  GF_GO(8, 32, 4, 256)
 #undef GF_GO
   return -3;
 }

@@ -227,6 +227,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
+                                        const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(smem_u32(p)));
+}
+
 template <bool FIRST>
 __global__ void __launch_bounds__(256)
 moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w,
@@ -284,20 +291,17 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
 #pragma unroll
     for (int kk = 0; kk < kTK; kk += 16) {
       uint32_t af[2][4], bfr[4][2];
+      // ldmatrix: A 16 x 16 (lanes 0-15 the rows, lanes 16-31 the second 8 of k); B two column
+      // tiles at once (lanes 0-7 / 8-15: the first tile's rows at k / k + 8, lanes 16-31 the second's)
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const __nv_bfloat16* base = &As[st][wm * 32 + i * 16 + g][kk + 2 * t];
-        af[i][0] = *reinterpret_cast<const uint32_t*>(base);
-        af[i][1] = *reinterpret_cast<const uint32_t*>(base + 8 * kTLd);
-        af[i][2] = *reinterpret_cast<const uint32_t*>(base + 8);
-        af[i][3] = *reinterpret_cast<const uint32_t*>(base + 8 * kTLd + 8);
-      }
+      for (int i = 0; i < 2; ++i)
+        ldsm_x4(af[i][0], af[i][1], af[i][2], af[i][3],
+                &As[st][wm * 32 + i * 16 + (lane & 15)][kk + ((lane >> 4) << 3)]);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __nv_bfloat16* base = &Ws[st][wn * 32 + j * 8 + g][kk + 2 * t];
-        bfr[j][0] = *reinterpret_cast<const uint32_t*>(base);
-        bfr[j][1] = *reinterpret_cast<const uint32_t*>(base + 8);
-      }
+      for (int jj = 0; jj < 2; ++jj)
+        ldsm_x4(bfr[2 * jj][0], bfr[2 * jj][1], bfr[2 * jj + 1][0], bfr[2 * jj + 1][1],
+                &Ws[st][wn * 32 + jj * 16 + (lane & 7) + ((lane >> 4) << 3)]
+                   [kk + (((lane >> 3) & 1) << 3)]);
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll

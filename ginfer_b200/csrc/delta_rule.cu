@@ -131,6 +131,7 @@ __global__ void delta_conv_state_kernel(const T* __restrict__ proj, int ld,
 
 constexpr int kRecurrenceThreads = 128;
 constexpr int kMaxColumnsPerBlock = 32;
+constexpr int kStages = 3;             // chunks of tokens in shared memory
 
 __device__ __forceinline__ void copy_async_4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -143,8 +144,8 @@ __device__ __forceinline__ void copy_async_wait() {
 
 // A block = (request, head, 128 / LP columns of S); LP lanes share a column, DPER rows each.  The
 // tokens' k, q, g rows (padded to Dp = LP * DPER floats, the padding zero), the block's v columns and
-// beta come through two stages of shared memory, CHUNK tokens each, asked for one chunk ahead with
-// cp.async.  LP = 4 where requests x heads x columns fill the device (decode batches); LP = 32
+// beta come through three stages of shared memory, CHUNK tokens each, asked for two chunks ahead
+// with cp.async.  LP = 4 where requests x heads x columns fill the device (decode batches); LP = 32
 // (a warp a column, eight columns a block) where they do not (one long prompt): a token is a chain
 // of dependent instructions for a warp, and with eight times the lanes a column the chain is short
 // and eight times as many warps share an SM's schedulers.
@@ -157,14 +158,14 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
                         DeltaDims dm, float* __restrict__ o) {
   constexpr int Dp = LP * DPER;
   constexpr int kTok = 3 * Dp + kMaxColumnsPerBlock + 4;      // floats a token in a stage
-  extern __shared__ __align__(16) float stage[];               // [2][CHUNK][kTok]
+  extern __shared__ __align__(16) float stage[];               // [kStages][CHUNK][kTok]
   constexpr int cols = THREADS / LP;
   const int b = blockIdx.x / dm.H, h = blockIdx.x - b * dm.H;
   const int part = threadIdx.x % LP, lc = threadIdx.x / LP;
   const int col0 = blockIdx.y * cols, col = col0 + lc;
   pdl_trigger();
   const int D = dm.D, Vd = dm.Vd;
-  for (int i = threadIdx.x; i < 2 * CHUNK * kTok; i += blockDim.x) stage[i] = 0.f;
+  for (int i = threadIdx.x; i < kStages * CHUNK * kTok; i += blockDim.x) stage[i] = 0.f;
   __syncthreads();
   pdl_wait();
   const int row0 = part * DPER;
@@ -181,8 +182,8 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   // 16-byte copies where rows allow it (a thread keeps the same piece of every token), else 4-byte
   const bool vec = (D & 3) == 0 && (Vd & 3) == 0 && (ncols & 3) == 0;
   const int dq = D >> 2, pieces = 3 * dq + (ncols >> 2);
-  auto ask = [&](int chunk) {                      // the chunk's tokens into stage chunk & 1
-    float* st = stage + (size_t)(chunk & 1) * CHUNK * kTok;
+  auto ask = [&](int chunk) {                      // the chunk's tokens into stage chunk % kStages
+    float* st = stage + (size_t)(chunk % kStages) * CHUNK * kTok;
     const int ta = t0 + chunk * CHUNK, n = min(CHUNK, t1 - ta);
     if (vec) {
       for (int e = threadIdx.x; e < pieces; e += blockDim.x) {
@@ -223,16 +224,19 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
     copy_async_commit();
   };
   const int nchunks = (t1 - t0 + CHUNK - 1) / CHUNK;
-  if (nchunks > 0) ask(0);
+  // two chunks are under way while a third is worked on (a group is committed every turn, empty
+  // ones too, so that "all but the last two" always means "chunk c has landed")
+  for (int c = 0; c < kStages - 1; ++c) {
+    if (c < nchunks) ask(c);
+    else copy_async_commit();
+  }
   for (int c = 0; c < nchunks; ++c) {
-    if (c + 1 < nchunks) {
-      ask(c + 1);
-      copy_async_wait<1>();
-    } else {
-      copy_async_wait<0>();
-    }
+    // the stage of chunk c + 2 held chunk c - 1, which every warp left at the last barrier
+    if (c + kStages - 1 < nchunks) ask(c + kStages - 1);
+    else copy_async_commit();
+    copy_async_wait<kStages - 1>();
     __syncthreads();
-    const float* st = stage + (size_t)(c & 1) * CHUNK * kTok;
+    const float* st = stage + (size_t)(c % kStages) * CHUNK * kTok;
     const int ta = t0 + c * CHUNK, n = min(CHUNK, t1 - ta);
     // The chunk's tokens, unrolled: the read-out o = S^T q of a token is off the chain that the
     // next token waits for (only u is on it), so its lane reduction is left until the chunk is
@@ -371,16 +375,18 @@ GF_EXPORT int gf_delta_recurrence(const float* qn, const float* kn, const float*
   if (H % G) return -3;
   const DeltaDims dm = dims_of(H, G, D, Vd, 1, state_stride, 0);
   auto st = (cudaStream_t)stream;
-  // few (request, head, column) triples: a warp a column instead of four lanes (see the kernel)
+  // few (request, head, column) triples: a warp (sixteen lanes for key sizes up to 64) a column
+  // instead of four lanes (see the kernel)
   const bool wide = (long long)B * H * ((Vd + 31) / 32) < 2 * 148;
-  const int threads = wide ? 256 : kRecurrenceThreads;
-  const int cols = threads / (wide ? 32 : 4);
+  const int lp = !wide ? 4 : (D <= 64 ? 16 : 32);
+  const int threads = lp == 32 ? 256 : kRecurrenceThreads;
+  const int cols = threads / lp;
   const dim3 grid(B * H, (Vd + cols - 1) / cols);
   const dim3 block(threads);
 #define GF_GO(DPER, LP, CHUNK, THREADS)                                                            \
-  if (wide == (LP == 32) && D <= LP * DPER) {                                                      \
+  if (lp == LP && D <= LP * DPER) {                                                                \
     const size_t smem =                                                                            \
-        (size_t)2 * CHUNK * (3 * LP * DPER + kMaxColumnsPerBlock + 4) * sizeof(float);             \
+        (size_t)kStages * CHUNK * (3 * LP * DPER + kMaxColumnsPerBlock + 4) * sizeof(float);       \
     return launch_kernel(delta_recurrence_kernel<DPER, LP, CHUNK, THREADS>, grid, block, smem, st,  \
                          qn, kn, v, g, beta, state, cu_seqlens, slot_ids, dm, o);                  \
   }
@@ -389,6 +395,7 @@ GF_EXPORT int gf_delta_recurrence(const float* qn, const float* kn, const float*
   GF_GO(16, 4, 8, kRecurrenceThreads)
   GF_GO(32, 4, 8, kRecurrenceThreads)
   GF_GO(64, 4, 4, kRecurrenceThreads)
+  GF_GO(4, 16, 8, kRecurrenceThreads)
   GF_GO(4, 32, 8, 256)
   GF_GO(8, 32, 4, 256)
 #undef GF_GO

@@ -445,23 +445,30 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o,
   pdl_wait();
   if (pair >= num_tokens * H) return;
   const int t = pair / H, h = pair - t * H;
-  float M = -INFINITY;
-  for (int z = 0; z < nsplit; ++z)
-    M = fmaxf(M, part_ml[2 * (((size_t)z * num_tokens + t) * H + h)]);
-  float L = 0.f;
-  for (int z = 0; z < nsplit; ++z) {
-    const size_t at = ((size_t)z * num_tokens + t) * H + h;
-    L += part_ml[2 * at + 1] * expf(part_ml[2 * at] - M);
+  constexpr int kMaxSplits = 16;
+  float w[kMaxSplits];                             // a share's weight exp(m_z - M), 0 if empty
+  float M = -INFINITY, L = 0.f;
+#pragma unroll
+  for (int z = 0; z < kMaxSplits; ++z) {
+    w[z] = z < nsplit ? part_ml[2 * (((size_t)z * num_tokens + t) * H + h)] : -INFINITY;
+    M = fmaxf(M, w[z]);
   }
+#pragma unroll
+  for (int z = 0; z < kMaxSplits; ++z) {
+    const float lz = z < nsplit ? part_ml[2 * (((size_t)z * num_tokens + t) * H + h) + 1] : 0.f;
+    w[z] = lz > 0.f ? expf(w[z] - M) : 0.f;
+    L += lz * w[z];
+  }
+  const float inv = 1.f / L;
   bf16* dst = out + ((size_t)h * num_tokens + t) * C;
+  const size_t step = (size_t)num_tokens * H * C;
+  const float* src = part_o + ((size_t)t * H + h) * C;
   for (int c = lane; c < C; c += 32) {
     float acc = 0.f;
-    for (int z = 0; z < nsplit; ++z) {
-      const size_t at = ((size_t)z * num_tokens + t) * H + h;
-      const float lz = part_ml[2 * at + 1];
-      if (lz > 0.f) acc += part_o[at * C + c] * expf(part_ml[2 * at] - M);
-    }
-    dst[c] = __float2bfloat16_rn(acc / L);
+#pragma unroll
+    for (int z = 0; z < kMaxSplits; ++z)
+      if (z < nsplit && w[z] > 0.f) acc = fmaf(src[z * step + c], w[z], acc);
+    dst[c] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -515,7 +522,7 @@ GF_EXPORT int gf_latent_attention(const float* q_lat, const float* q_rot, const 
         return e;
       });
       if (rc) return rc;
-      if (nsplit < 1 || (nsplit > 1 && (!part_o || !part_ml))) nsplit = 1;
+      if (nsplit < 1 || nsplit > 16 || (nsplit > 1 && (!part_o || !part_ml))) nsplit = 1;
       const dim3 grid(T, (H + 15) / 16, nsplit), block(kMmaWarps * 32);
       auto st = (cudaStream_t)stream;
       int rc2 = -3;

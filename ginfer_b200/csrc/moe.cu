@@ -1,18 +1,22 @@
 // Routed feed-forward (mixture of experts) without a host round trip: every kernel reads the
 // routing from device memory, so a step can be captured in a CUDA graph.
 //
-//   moe_route_kernel    a warp a token: scores = softmax(router logits) in fp32 over all experts,
-//                       the `top` largest chosen (lowest index among equals), their scores kept as
-//                       weights (optionally renormalised over the chosen ones).
+//   moe_route_kernel    a warp a token: scores = softmax(router logits) in fp32 over all experts
+//                       (or the sigmoid of each logit), the `top` largest chosen (lowest index
+//                       among equals), their scores kept as weights (optionally renormalised over
+//                       the chosen ones).
 //   moe_plan_kernel     one block: (token, choice) pairs counted per expert, the experts' ranges in
 //                       the sorted order, each pair's place, and the list of row tiles (expert,
 //                       first row) that the grouped products walk over.
 //   moe_gemm_mma_kernel the grouped products of the bf16 path, on the tensor cores (see there).
 //   moe_gemm_kernel     (32-bit path, and sizes the other refuses) grouped product over the sorted pairs, a block a (row tile, column tile):
 //                       FIRST: rows gathered from the tokens, W = the expert's row-interleaved
-//                       gate/up matrix, epilogue = clamped sigmoid-gated GLU; else rows = the first
-//                       product's output, W = the expert's down matrix, fp32 out.  The reduction
-//                       runs in a fixed order, so a pair's result does not depend on the batch.
+//                       gate/up matrix, epilogue = clamped sigmoid-gated GLU (MODE 1), or W = the
+//                       expert's up matrix, epilogue = relu(w * acc)^2 with the pair's routing
+//                       weight w, which is the product of the row scaled by w (MODE 2); else
+//                       (MODE 0) rows = the first product's output, W = the expert's down matrix,
+//                       fp32 out.  The reduction runs in a fixed order, so a pair's result does
+//                       not depend on the batch.
 //   moe_combine_kernel  out[t] = sum over the token's choices, in the order chosen, of weight *
 //                       the pair's row.
 #include "common.cuh"
@@ -23,7 +27,8 @@ constexpr int kMaxExperts = 256;
 constexpr int kRouteSlots = kMaxExperts / 32;
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int top,
-                                 int renorm, int* __restrict__ idx, float* __restrict__ wgt) {
+                                 int renorm, int sigmoid, int* __restrict__ idx,
+                                 float* __restrict__ wgt) {
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   pdl_trigger();
   pdl_wait();
@@ -40,10 +45,11 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < kRouteSlots; ++i) {
-    s[i] = lane + 32 * i < E ? expf(s[i] - mx) : -1.f;       // -1: no expert, or taken
+    const float sc = sigmoid ? 1.f / (1.f + expf(-s[i])) : expf(s[i] - mx);
+    s[i] = lane + 32 * i < E ? sc : -1.f;                    // -1: no expert, or taken
     sum += s[i] > 0.f ? s[i] : 0.f;
   }
-  sum = warp_sum(sum);
+  sum = sigmoid ? 1.f : warp_sum(sum);
   float chosen_sum = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -1.f;
@@ -130,15 +136,17 @@ __device__ __forceinline__ float clamped_glu(float g, float u, float limit, floa
 
 constexpr int kBM = 32, kBN = 64, kBK = 32;
 
-// FIRST: a [T, K] tokens (row of sorted place s = pair_of_pos[s] / top), w [E, 2F, K] (gate row,
-// up row, ...), out [P, F] of type T.  Else: a [P, K] (T), w [E, N, K], out [P, N] fp32.
-template <typename T, bool FIRST>
+// MODE 1: a [T, K] tokens (row of sorted place s = pair_of_pos[s] / top), w [E, 2F, K] (gate row,
+// up row, ...), out [P, F] of type T.  MODE 2: the same rows, w [E, F, K], out [P, F] of type T =
+// relu(row_w[pair] * acc)^2 (row_w null: 1).  MODE 0: a [P, K] (T), w [E, N, K], out [P, N] fp32.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, int N, int K,
                 const int* __restrict__ offsets, const int* __restrict__ pair_of_pos, int top,
                 const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                 const int* __restrict__ num_tiles, void* __restrict__ out_, float limit,
-                float alpha, float up_shift) {
+                float alpha, float up_shift, const float* __restrict__ row_w) {
+  constexpr bool FIRST = MODE != 0;
   __shared__ float As[kBM][kBK + 1], Ws[kBN][kBK + 1];
   __shared__ int src_row[kBM];
   pdl_trigger();
@@ -183,7 +191,18 @@ moe_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, int N
     const int r = 2 * ty + i;
     if (r >= rows) continue;
     const size_t s = (size_t)(row0 + r);
-    if (FIRST) {
+    if (MODE == 2) {
+      T* out = (T*)out_;
+      const float rw = row_w ? row_w[pair_of_pos[s]] : 1.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + 4 * tx + j;
+        if (n < N) {
+          const float u = fmaxf(to_f32(from_f32<T>(acc[i][j] * rw)), 0.f);
+          out[s * N + n] = from_f32<T>(u * u);
+        }
+      }
+    } else if (MODE == 1) {
       T* out = (T*)out_;
       const int F = N / 2;
 #pragma unroll
@@ -234,14 +253,15 @@ __device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2
                : "r"(smem_u32(p)));
 }
 
-template <bool FIRST>
+template <int MODE>
 __global__ void __launch_bounds__(256)
 moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w,
                     int N, int K, const int* __restrict__ offsets,
                     const int* __restrict__ pair_of_pos, int top,
                     const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                     const int* __restrict__ num_tiles, void* __restrict__ out_, float limit,
-                    float alpha, float up_shift) {
+                    float alpha, float up_shift, const float* __restrict__ row_w) {
+  constexpr bool FIRST = MODE != 0;
   __shared__ __align__(16) __nv_bfloat16 As[kTStages][kTM][kTLd];
   __shared__ __align__(16) __nv_bfloat16 Ws[kTStages][kTN][kTLd];
   __shared__ int src_row[kTM];
@@ -317,11 +337,18 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
       const int r = wm * 32 + i * 16 + g + 8 * hh;
       if (r >= rows) continue;
       const size_t s = (size_t)(row0 + r);
+      const float rw = (MODE == 2 && row_w) ? row_w[pair_of_pos[s]] : 1.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int n = n0 + wn * 32 + j * 8 + 2 * t;
         const float c0 = acc[i][j][2 * hh], c1 = acc[i][j][2 * hh + 1];
-        if (FIRST) {
+        if (MODE == 2) {
+          __nv_bfloat16* out = (__nv_bfloat16*)out_ + s * N;
+          const float u0 = fmaxf(to_f32(from_f32<__nv_bfloat16>(c0 * rw)), 0.f);
+          const float u1 = fmaxf(to_f32(from_f32<__nv_bfloat16>(c1 * rw)), 0.f);
+          if (n < N) out[n] = from_f32<__nv_bfloat16>(u0 * u0);
+          if (n + 1 < N) out[n + 1] = from_f32<__nv_bfloat16>(u1 * u1);
+        } else if (MODE == 1) {
           if (n < N) {
             const float gt = to_f32(from_f32<__nv_bfloat16>(c0)), up = to_f32(from_f32<__nv_bfloat16>(c1));
             ((__nv_bfloat16*)out_)[s * (N / 2) + n / 2] =
@@ -346,7 +373,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
   for (int n = threadIdx.x; n < N; n += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k)
-      acc = fmaf(wgt[(size_t)t * top + k], y[(size_t)pos_of_pair[(size_t)t * top + k] * N + n], acc);
+      acc = fmaf(wgt ? wgt[(size_t)t * top + k] : 1.f,
+                 y[(size_t)pos_of_pair[(size_t)t * top + k] * N + n], acc);
     out[(size_t)t * N + n] = from_f32<T>(acc);
   }
 }
@@ -361,12 +389,13 @@ GF_DEFINE_PDL_SWITCH
 // Rows of a tile: of the plain kernel (tensor_cores == 0) or of the tensor-core kernel.
 GF_EXPORT int gf_moe_tile_rows(int tensor_cores) { return tensor_cores ? kTM : kBM; }
 
-GF_EXPORT int gf_moe_route(const float* logits, int T, int E, int top, int renorm, int* idx,
-                           float* wgt, void* stream) {
+// sigmoid != 0: a score is the sigmoid of its logit instead of the softmax over all experts.
+GF_EXPORT int gf_moe_route(const float* logits, int T, int E, int top, int renorm, int sigmoid,
+                           int* idx, float* wgt, void* stream) {
   if (T <= 0) return 0;
   if (E > kMaxExperts || top > E || top > 32) return -3;
   return launch_kernel(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream,
-                       logits, T, E, top, renorm, idx, wgt);
+                       logits, T, E, top, renorm, sigmoid, idx, wgt);
 }
 
 GF_EXPORT int gf_moe_plan(const int* idx, int P, int E, int tile_rows, int* offsets,
@@ -379,36 +408,40 @@ GF_EXPORT int gf_moe_plan(const int* idx, int P, int E, int tile_rows, int* offs
                        num_tiles);
 }
 
-// first != 0: gate/up product with the activation; out [P, N / 2] (dtype).  Else down: out fp32.
+// first 1: gate/up product with the clamped GLU; out [P, N / 2] (dtype).  first 2: up product with
+// relu(row_w * .)^2; out [P, N] (dtype); row_w [P] by pair, or null.  first 0: down; out fp32.
 GF_EXPORT int gf_moe_gemm(const void* a, int lda, const void* w, int N, int K, const int* offsets,
                           const int* pair_of_pos, int top, const int* tile_expert,
                           const int* tile_row0, const int* num_tiles, int max_tiles, void* out,
-                          int first, float limit, float alpha, float up_shift, int dtype,
-                          int tensor_cores, void* stream) {
+                          int first, float limit, float alpha, float up_shift,
+                          const float* row_w, int dtype, int tensor_cores, void* stream) {
   if (max_tiles <= 0) return 0;
   auto st = (cudaStream_t)stream;
   if (tensor_cores) {
     if (dtype != GF_BF16 || K % 8 || lda % 8 || (uintptr_t)a % 16 || (uintptr_t)w % 16) return -3;
     const dim3 tgrid(max_tiles, (N + kTN - 1) / kTN), tblock(256);
-    if (first)
-      return launch_kernel(moe_gemm_mma_kernel<true>, tgrid, tblock, 0, st, (const bf*)a, lda,
-                           (const bf*)w, N, K, offsets, pair_of_pos, top, tile_expert, tile_row0,
-                           num_tiles, out, limit, alpha, up_shift);
-    return launch_kernel(moe_gemm_mma_kernel<false>, tgrid, tblock, 0, st, (const bf*)a, lda,
-                         (const bf*)w, N, K, offsets, pair_of_pos, top, tile_expert, tile_row0,
-                         num_tiles, out, limit, alpha, up_shift);
+#define GF_TC(MODE)                                                                               \
+  return launch_kernel(moe_gemm_mma_kernel<MODE>, tgrid, tblock, 0, st, (const bf*)a, lda,          \
+                       (const bf*)w, N, K, offsets, pair_of_pos, top, tile_expert, tile_row0,       \
+                       num_tiles, out, limit, alpha, up_shift, row_w)
+    if (first == 2) GF_TC(2);
+    if (first) GF_TC(1);
+    GF_TC(0);
+#undef GF_TC
   }
   const dim3 grid(max_tiles, (N + kBN - 1) / kBN), block(256);
-#define GF_GO(T, FIRST)                                                                          \
-  return launch_kernel(moe_gemm_kernel<T, FIRST>, grid, block, 0, st, (const T*)a, lda,          \
+#define GF_GO(T, MODE)                                                                           \
+  return launch_kernel(moe_gemm_kernel<T, MODE>, grid, block, 0, st, (const T*)a, lda,           \
                        (const T*)w, N, K, offsets, pair_of_pos, top, tile_expert, tile_row0,      \
-                       num_tiles, out, limit, alpha, up_shift)
+                       num_tiles, out, limit, alpha, up_shift, row_w)
   if (dtype == GF_F32) {
-    if (first) GF_GO(float, true);
-    GF_GO(float, false);
+    if (first == 2) GF_GO(float, 2);
+    if (first) GF_GO(float, 1);
+    GF_GO(float, 0);
   }
-  if (first) GF_GO(bf, true);
-  GF_GO(bf, false);
+  if (first == 2) GF_GO(bf, 2);
+  if (first) GF_GO(bf, 1);
+  GF_GO(bf, 0);
 #undef GF_GO
 }
 

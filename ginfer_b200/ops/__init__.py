@@ -336,3 +336,4 @@ def bmm_f32_out(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 from .linear import GatedLinear, Linear, add_to  # noqa: E402,F401
+from . import prenorm  # noqa: E402,F401

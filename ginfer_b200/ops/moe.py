@@ -23,17 +23,21 @@ def on_tensor_cores(dtype: torch.dtype, *reductions: int) -> bool:
     return dtype == torch.bfloat16 and all(k % 8 == 0 for k in reductions)
 
 
-def route(logits: torch.Tensor, top: int, renormalize: bool):
-    """fp32 ``logits [T, E]`` -> ``(experts [T, top] int32, weights [T, top] fp32)``: softmax over
-    all experts, the ``top`` largest, lowest index among equals."""
+def route(logits: torch.Tensor, top: int, renormalize: bool, score: str = "softmax"):
+    """fp32 ``logits [T, E]`` -> ``(experts [T, top] int32, weights [T, top] fp32)``: scores =
+    softmax over all experts (``score="softmax"``) or each logit's sigmoid (``"sigmoid"``), the
+    ``top`` largest, lowest index among equals."""
+    if score not in ("softmax", "sigmoid"):
+        raise ValueError(f"router scores are 'softmax' or 'sigmoid', not {score!r}")
     _cuda(logits)
     assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
     T, E = logits.shape
     idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     wgt = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    f = _fn("moe", "gf_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                    c_void_p])
-    rc = f(_p(logits), T, E, int(top), int(bool(renormalize)), _p(idx), _p(wgt), _stream())
+    f = _fn("moe", "gf_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                    c_void_p, c_void_p])
+    rc = f(_p(logits), T, E, int(top), int(bool(renormalize)), int(score == "sigmoid"), _p(idx),
+           _p(wgt), _stream())
     if rc == -3:
         raise ValueError(f"the router kernel takes up to 256 experts and 32 choices, got {E}, {top}")
     _ok(rc, "moe_route")
@@ -79,7 +83,24 @@ def grouped_glu(x: torch.Tensor, w_gate_up: torch.Tensor, plan: Plan, limit: flo
     assert x.dtype == w_gate_up.dtype and x.stride(1) == 1 and x.shape[1] == K
     assert w_gate_up.is_contiguous()
     out = torch.empty((plan.pairs, N // 2), dtype=x.dtype, device=x.device)
-    _gemm(x, w_gate_up, plan, out, True, limit, alpha, up_shift)
+    _gemm(x, w_gate_up, plan, out, 1, limit, alpha, up_shift)
+    return out
+
+
+def grouped_relu2(x: torch.Tensor, w_up: torch.Tensor, plan: Plan, row_weights=None
+                  ) -> torch.Tensor:
+    """``x [T, K]``, ``w_up [E, F, K]`` -> ``relu(w * (x W^T))^2`` of every pair, in sorted order:
+    ``[P, F]``; ``row_weights [T, top]`` fp32 gives each pair's ``w`` (the product of the row
+    scaled by ``w``), ``None`` means 1."""
+    _cuda(x, w_up, row_weights)
+    E, N, K = w_up.shape
+    assert x.dtype == w_up.dtype and x.stride(1) == 1 and x.shape[1] == K
+    assert w_up.is_contiguous()
+    if row_weights is not None:
+        assert row_weights.dtype == torch.float32 and row_weights.is_contiguous()
+        assert row_weights.numel() == plan.pairs
+    out = torch.empty((plan.pairs, N), dtype=x.dtype, device=x.device)
+    _gemm(x, w_up, plan, out, 2, 0.0, 0.0, 0.0, row_weights)
     return out
 
 
@@ -89,23 +110,25 @@ def grouped_down(y: torch.Tensor, w_down: torch.Tensor, plan: Plan) -> torch.Ten
     E, N, K = w_down.shape
     assert y.dtype == w_down.dtype and y.is_contiguous() and y.shape == (plan.pairs, K)
     out = torch.empty((plan.pairs, N), dtype=torch.float32, device=y.device)
-    _gemm(y, w_down, plan, out, False, 0.0, 0.0, 0.0)
+    _gemm(y, w_down, plan, out, 0, 0.0, 0.0, 0.0)
     return out
 
 
-def _gemm(a, w, plan, out, first, limit, alpha, up_shift):
+def _gemm(a, w, plan, out, first, limit, alpha, up_shift, row_w=None):
     f = _fn("moe", "gf_moe_gemm",
             [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
-             c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float, c_int,
-             c_int, c_void_p])
+             c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float, c_void_p,
+             c_int, c_int, c_void_p])
     _ok(f(_p(a), a.stride(0), _p(w), w.shape[1], w.shape[2], _p(plan.offsets),
           _p(plan.pair_of_pos), plan.top, _p(plan.tile_expert), _p(plan.tile_row0),
           _p(plan.num_tiles), plan.max_tiles, _p(out), int(first), float(limit), float(alpha),
-          float(up_shift), _code(a.dtype), int(plan.tensor_cores), _stream()), "moe_gemm")
+          float(up_shift), _p(row_w), _code(a.dtype), int(plan.tensor_cores), _stream()),
+        "moe_gemm")
 
 
-def combine(y: torch.Tensor, plan: Plan, weights: torch.Tensor, num_tokens: int) -> torch.Tensor:
-    """``out[t] = sum_k weights[t, k] * y[place of pair (t, k)]``, fp32."""
+def combine(y: torch.Tensor, plan: Plan, weights, num_tokens: int) -> torch.Tensor:
+    """``out[t] = sum_k weights[t, k] * y[place of pair (t, k)]``, fp32 (``weights`` ``None``:
+    the plain sum)."""
     N = y.shape[1]
     out = torch.empty((num_tokens, N), dtype=torch.float32, device=y.device)
     f = _fn("moe", "gf_moe_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,

@@ -3,8 +3,9 @@ from .base import (Block, Embedding, FeedForward, Head, LazyNorm, Mixer, Norm, P
                    PagedKVSpec, Part, PositionEncoding, StateBinding, StateSpec, StepContext, Summed,
                    TensorSpec,
                    make_part, register_block, register_feed_forward, register_mixer,
-                   register_norm, register_part, register_position)
+                   register_norm, register_part, register_position, register_stream_input,
+                   StreamInput)
 from .plan import LayerSpec, ModelPlan, PartSpec, RunEntry, sequential_run
-from . import (attention, block, delta_rule, embedding, feed_forward, latent_attention, norm,  # noqa: F401
-               position, routed)
+from . import (attention, block, delta_rule, embedding, feed_forward, gated_attention,  # noqa: F401
+               latent_attention, norm, position, routed, stream_input)
 from .model import DecoderModel

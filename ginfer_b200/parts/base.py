@@ -28,10 +28,15 @@ class TensorSpec:
     * ``norm``: like ``bias`` but drawn 1 + N(0, 0.02).
     * ``f32``: a small tensor that enters 32-bit arithmetic (a router, decay constants, norm
       weights stored around zero); always kept in 32-bit; N(0, 0.02).
+    * ``norm32``: a norm weight that is always kept in 32-bit; drawn 1 + N(0, 0.02).
     * ``int``: integer table, kept as int32; drawn uniform in ``[0, int_high)``.
 
     A size of ``-1`` in ``shape`` stands for "whatever the file has" (a rank that only the
     tensor's own shape gives); random weights cannot be drawn for such a tensor.
+
+    A name that starts with ``/`` is a tensor of the whole model, not of the part's scope: it is
+    looked up without the layer prefix, and several parts may name the same one (a table that
+    every layer reads a slice of).
     """
     name: str
     shape: tuple[int, ...]
@@ -172,6 +177,12 @@ class Norm(Part):
         into the product that consumes it; ``None`` otherwise."""
         return None
 
+    def fused(self) -> tuple | None:
+        """``(kind, weight, bias or None, eps)`` with fp32 tensors if the kernel that updates a
+        32-bit stream can apply this norm in the same pass (``ops.prenorm.NORM_LAYER`` /
+        ``NORM_RMS``); ``None`` (the default) if it cannot."""
+        return None
+
     def fold_weight(self) -> torch.Tensor | None:
         """The weight ``gamma`` if this norm is ``x * gamma / rms(x)`` and so can be split into a
         multiplication by ``gamma`` in the product before it and one by ``1 / rms`` in the product
@@ -234,6 +245,26 @@ class Block(Part):
         return None
 
 
+class StreamInput(Part):
+    """Something added to the residual stream that is not a sublayer's output: a vector that
+    depends on the token, on the pass of a loop, or on the embedding output.  Two places use such
+    parts: a block may end with one (``forward``), and a run of the plan may start with one
+    (``enter``: :attr:`RunEntry.enter`)."""
+
+    wants_act = False      # forward() reads the stream rounded to the activation dtype
+
+    def forward(self, x: torch.Tensor, act: torch.Tensor | None, ctx: StepContext, mult: float,
+                then: "Norm | None" = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """``x`` fp32 ``[T, H]`` -> ``(x', then(x') or None)``; ``act``: ``x`` in the activation
+        dtype if the part asked for it; ``mult``: the layer's residual multiplier."""
+        raise NotImplementedError
+
+    def enter(self, x: torch.Tensor, ctx: StepContext, embedding_output: torch.Tensor,
+              index: int) -> torch.Tensor:
+        """``x`` before a run of the plan -> ``x'``; ``index``: the entry's number."""
+        raise NotImplementedError
+
+
 class Embedding(Part):
     def forward(self, token_ids: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
@@ -246,7 +277,8 @@ class Head(Part):
 
 
 # ----------------------------------------------------------------------------- registries
-_FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+_FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head",
+             "stream_input")
 _REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {f: {} for f in _FAMILIES}
 
 
@@ -283,3 +315,7 @@ def register_position(kind, factory):
 
 def register_block(kind, factory):
     register_part("block", kind, factory)
+
+
+def register_stream_input(kind, factory):
+    register_part("stream_input", kind, factory)

@@ -145,3 +145,98 @@ class OutputNormBlock(Block):
 
 
 register_block("outnorm", OutputNormBlock)
+
+
+class ScaledPreNormBlock(Block):
+    """Pre-norm sublayers on a 32-bit stream whose outputs are scaled before they are added:
+    ``x <- x + mult * s1 * mixer(norm1(x))``, ``x <- x + mult * s2 * ff(norm2(x))`` with
+    per-channel scales ``s1``, ``s2`` (tensors of the layer; a name of ``None`` means no scale),
+    then, if the layer has one, a stream input (``after``, family ``stream_input``).  A layer
+    without a feed-forward is the first line alone.
+
+    Each addition is one kernel that also writes what the next step reads: the norm of the new
+    stream for the sublayer behind it (also the first norm of the NEXT run, ``then``, which
+    travels there in ``ctx.extras["prenormed"]``), or its rounding to the activation dtype for a
+    stream input that multiplies it by a matrix."""
+
+    takes_next_norm = True
+
+    def __init__(self, layer_spec, residual_mult: float = 1.0, mixer_scale: str | None = None,
+                 feed_forward_scale: str | None = None, after=None):
+        self.spec = layer_spec
+        self.mult = float(residual_mult)
+        self.mixer_norm = make_part("norm", layer_spec.mixer_norm)
+        self.mixer = make_part("mixer", layer_spec.mixer)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward_norm = make_part("norm", layer_spec.feed_forward_norm)
+            self.feed_forward = make_part("feed_forward", layer_spec.feed_forward)
+        self.after = make_part("stream_input", after) if after is not None else None
+        self.scale_names = (mixer_scale, feed_forward_scale if self.feed_forward else None)
+        self.scales = [None, None]
+        self.size = None
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm,
+                                 self.feed_forward, self.after) if p is not None)
+
+    def tensor_specs(self):
+        from .base import TensorSpec
+        out = []
+        for p in self.parts():
+            out.extend(p.tensor_specs())
+        width = next(s.shape[0] for s in self.mixer_norm.tensor_specs())
+        out += [TensorSpec(n, (width,), "f32") for n in self.scale_names if n]
+        return out
+
+    def first_norm(self):
+        return self.mixer_norm
+
+    def load(self, tensors, dtype, device):
+        for p in self.parts():
+            p.load(tensors, dtype, device)
+        self.scales = [tensors[n].float().contiguous() if n else None for n in self.scale_names]
+
+    def _add(self, x, y, scale, ctx, then, want_act=False):
+        """``x + mult * scale * y`` -> ``(x', x' in the activation dtype or None, then(x'))``."""
+        from ..ops import prenorm
+        fused = then.fused() if then is not None else None
+        if then is not None and fused is None:       # a norm the kernel cannot apply: on its own
+            x, act, _ = prenorm.stream_update(x, ctx.dtype, y=y, scale=scale, mult=self.mult,
+                                              want_act=want_act)
+            return x, act, then.forward(x, None, want_sum=False, out_dtype=ctx.dtype)[1]
+        kw = {}
+        if fused is not None:
+            kw = dict(norm=fused[0], norm_weight=fused[1], norm_bias=fused[2], norm_eps=fused[3])
+        return prenorm.stream_update(x, ctx.dtype, y=y, scale=scale, mult=self.mult,
+                                     want_act=want_act, **kw)
+
+    def forward(self, x, delta, ctx, cache, then=None):
+        if delta is not None:
+            x = x.float() + delta.float()
+        elif x.dtype != torch.float32:
+            x = x.float()
+        kept = ctx.extras.pop("prenormed", None)
+        if kept is not None and kept[0] is x and kept[1] is self.mixer_norm:
+            n = kept[2]
+        else:
+            n = self.mixer_norm.forward(x, None, want_sum=False, out_dtype=ctx.dtype)[1]
+        a = self.mixer.forward(n, ctx, cache)
+        act_for_after = self.after is not None and self.after.wants_act
+        n_next = None
+        if self.feed_forward is not None:
+            x, _, n2 = self._add(x, a, self.scales[0], ctx, self.feed_forward_norm)
+            f = self.feed_forward.forward(n2, ctx)
+            x, act, n_next = self._add(x, f, self.scales[1], ctx,
+                                       then if self.after is None else None, act_for_after)
+        else:
+            x, act, n_next = self._add(x, a, self.scales[0], ctx,
+                                       then if self.after is None else None, act_for_after)
+        if self.after is not None:
+            x, n_next = self.after.forward(x, act, ctx, self.mult, then)
+        if n_next is not None:
+            ctx.extras["prenormed"] = (x, then, n_next)
+        return x, None
+
+
+register_block("scaled_prenorm", ScaledPreNormBlock)

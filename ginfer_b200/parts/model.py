@@ -21,6 +21,7 @@ class DecoderModel:
         self.blocks = [make_part("block", ls.block, layer_spec=ls) for ls in plan.layers]
         self.final_norm = make_part("norm", plan.final_norm)
         self.head = make_part("head", plan.head)
+        self.stream_inputs = [make_part("stream_input", s) for s in plan.stream_inputs]
         self.dtype: torch.dtype | None = None
         self.device: torch.device | None = None
 
@@ -28,10 +29,28 @@ class DecoderModel:
     def tensor_specs(self) -> list[TensorSpec]:
         """Every tensor of the model under its full name."""
         out = list(self.embedding.tensor_specs())
+        shared: dict[str, TensorSpec] = {}
+
+        def whole_model(s: TensorSpec) -> None:
+            # a tensor of the whole model ("/name"): several parts may name it, alike
+            g = TensorSpec(s.name[1:], s.shape, s.role, s.int_high)
+            if shared.setdefault(g.name, g) != g:
+                raise ValueError(f"parts disagree about the tensor {g.name!r}: {shared[g.name]} "
+                                 f"and {g}")
         for ls, blk in zip(self.plan.layers, self.blocks):
             pre = ls.prefix + "." if ls.prefix else ""
-            out += [TensorSpec(pre + s.name, s.shape, s.role, s.int_high)
-                    for s in blk.tensor_specs()]
+            for s in blk.tensor_specs():
+                if s.name.startswith("/"):
+                    whole_model(s)
+                else:
+                    out.append(TensorSpec(pre + s.name, s.shape, s.role, s.int_high))
+        for part in self.stream_inputs:
+            for s in part.tensor_specs():
+                if s.name.startswith("/"):
+                    whole_model(s)
+                else:
+                    out.append(s)
+        out += list(shared.values())
         out += self.final_norm.tensor_specs()
         out += self.head.tensor_specs()
         names = [s.name for s in out]
@@ -44,10 +63,14 @@ class DecoderModel:
              device: torch.device) -> None:
         self.dtype, self.device = dtype, device
         self.embedding.load(tensors, dtype, device)
+        whole = {"/" + k: v for k, v in tensors.items()}       # tensors of the whole model
         for ls, blk in zip(self.plan.layers, self.blocks):
             pre = ls.prefix + "." if ls.prefix else ""
             local = {k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)}
+            local.update(whole)
             blk.load(local, dtype, device)
+        for part in self.stream_inputs:
+            part.load({**tensors, **whole}, dtype, device)
         self.final_norm.load(tensors, dtype, device)
         self.head.load(tensors, dtype, device)
 
@@ -72,10 +95,15 @@ class DecoderModel:
         Returns fp32 logits ``[R, vocab]`` at ``ctx.logit_rows``."""
         delta = None
         x = self.embedding.forward(ctx.token_ids, ctx)
+        embedded = x
         run = self.plan.run
         for i, e in enumerate(run):
             blk = self.blocks[e.layer]
-            if blk.takes_next_norm and i + 1 < len(run):
+            if e.enter is not None:
+                if delta is not None:
+                    x, delta = x.float() + delta.float(), None
+                x = self.stream_inputs[e.enter[0]].enter(x, ctx, embedded, e.enter[1])
+            if blk.takes_next_norm and i + 1 < len(run) and run[i + 1].enter is None:
                 # the block may prepare the input of the norm that the next run starts with
                 x, delta = blk.forward(x, delta, ctx, bind_cache(e),
                                        then=self.blocks[run[i + 1].layer].first_norm())

@@ -52,4 +52,50 @@ class RMSNorm(Norm):
         return self.weight if not self.weight_offset else None
 
 
+    def fused(self):
+        if self.weight_offset or self.weight.dtype != torch.float32:
+            return None
+        return ops.prenorm.NORM_RMS, self.weight, None, self.eps
+
+
 register_norm("rmsnorm", RMSNorm)
+
+
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w + b`` with the variance as the mean of the squared
+    deviations; mean, variance and the result in 32-bit, weight and bias kept in 32-bit.  The
+    input is the fp32 residual stream; a ``delta`` still to be added is added in the same pass."""
+
+    def __init__(self, size: int, eps: float, weight_name: str = "weight",
+                 bias_name: str | None = "bias"):
+        self.size, self.eps = int(size), float(eps)
+        self.weight_name, self.bias_name = weight_name, bias_name
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def tensor_specs(self):
+        out = [TensorSpec(self.weight_name, (self.size,), "norm32")]
+        if self.bias_name:
+            out.append(TensorSpec(self.bias_name, (self.size,), "f32"))
+        return out
+
+    def load(self, tensors, dtype, device):
+        self.weight = tensors[self.weight_name].float().contiguous()
+        self.bias = tensors[self.bias_name].float().contiguous() if self.bias_name else None
+
+    def fused(self):
+        return ops.prenorm.NORM_LAYER, self.weight, self.bias, self.eps
+
+    def forward(self, x, delta=None, rows=None, want_sum=True, out_dtype=None):
+        act = out_dtype or (x.dtype if delta is None else delta.dtype)
+        if x.dtype != torch.float32:
+            x = x.float()
+        plain = delta is None and rows is None      # then the sum is x itself
+        s, _, n = ops.prenorm.stream_update(
+            x, act, y=delta, rows=rows, want_out=want_sum and not plain,
+            norm=ops.prenorm.NORM_LAYER, norm_weight=self.weight, norm_bias=self.bias,
+            norm_eps=self.eps)
+        return (x if plain and want_sum else s), n
+
+
+register_norm("layernorm", LayerNorm)

@@ -37,10 +37,14 @@ class LayerSpec:
 class RunEntry:
     """One run of a layer.  ``layer`` indexes :attr:`ModelPlan.layers` (a layer may be named
     twice).  ``cache`` names the cache this run uses: by default a cache of its own; a run with
-    ``write_cache=False`` only reads the cache another run has written earlier in the step."""
+    ``write_cache=False`` only reads the cache another run has written earlier in the step.
+    ``enter = (i, n)``: before this run the stream passes through
+    :attr:`ModelPlan.stream_inputs` ``[i]`` as its entry number ``n`` (the start of a pass of a
+    loop, say)."""
     layer: int
     cache: int
     write_cache: bool = True
+    enter: tuple[int, int] | None = None
 
 
 @dataclass(frozen=True)
@@ -54,6 +58,7 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     eos_token_ids: tuple[int, ...] = ()
+    stream_inputs: tuple[PartSpec, ...] = ()   # parts that runs enter through (RunEntry.enter)
     ignored_tensors: tuple[str, ...] = ()     # regular expressions of tensor names to pass over
 
     def validate(self) -> None:
@@ -62,6 +67,9 @@ class ModelPlan:
             if not (0 <= e.layer < len(self.layers)):
                 raise ValueError(f"run[{pos}] names layer {e.layer}, but there are "
                                  f"{len(self.layers)} layers")
+            if e.enter is not None and not (0 <= e.enter[0] < len(self.stream_inputs)):
+                raise ValueError(f"run[{pos}] enters through stream input {e.enter[0]}, but "
+                                 f"there are {len(self.stream_inputs)}")
             if e.write_cache:
                 if e.cache in writers:
                     raise ValueError(f"run[{pos}] and run[{writers[e.cache]}] both write cache "

@@ -52,5 +52,46 @@ class NoPosition(PositionEncoding):
         return None, 0
 
 
+class PairRotary(PositionEncoding):
+    """Rotation of channel pairs by ``position * f_i`` with ``f_i = base^(-2i/dims)`` over the
+    first ``dims`` channels of a head; the pairs are neighbours ``(2i, 2i+1)`` (``interleaved``) or
+    halves ``(i, i + dims/2)``.  ``scaling = {factor, low, high, original}`` stretches the long
+    wavelengths: with ``l = 2 pi / f``, ``f`` stays where ``l < original/high``, becomes
+    ``f / factor`` where ``l > original/low`` and ``(1 - s) f / factor + s f`` with
+    ``s = (original/l - low) / (high - low)`` in between.  Nothing is tabulated by position: the
+    mixer's kernel forms ``float(p) * f_i`` in 32-bit and takes sine and cosine of it."""
+
+    def __init__(self, dims: int, base: float, scaling=None, interleaved: bool = True):
+        self.dims, self.base = int(dims), float(base)
+        if self.dims % 2 or self.dims < 0:
+            raise ValueError(f"{self.dims} rotated channels: must be an even number")
+        self.scaling = None if scaling is None else {k: float(scaling[k]) for k in
+                                                     ("factor", "low", "high", "original")}
+        if self.scaling is not None and self.scaling["high"] == self.scaling["low"]:
+            raise ValueError("frequency scaling needs high != low")
+        self.interleaved = bool(interleaved)
+        self._freqs: torch.Tensor | None = None
+
+    def host_frequencies(self) -> np.ndarray:
+        i = np.arange(self.dims // 2, dtype=np.float64)
+        f = np.power(np.float64(self.base), -2.0 * i / max(self.dims, 1))
+        sc = self.scaling
+        if sc is not None:
+            wave = 2.0 * np.pi / f
+            ramp = (sc["original"] / wave - sc["low"]) / (sc["high"] - sc["low"])
+            mid = (1.0 - ramp) * f / sc["factor"] + ramp * f
+            f = np.where(wave < sc["original"] / sc["high"], f,
+                         np.where(wave > sc["original"] / sc["low"], f / sc["factor"], mid))
+        return f.astype(np.float32)
+
+    def load(self, tensors, dtype, device):
+        self._freqs = torch.from_numpy(self.host_frequencies()).to(device)
+
+    def frequencies(self) -> torch.Tensor:
+        """fp32 ``[dims / 2]`` on the device."""
+        return self._freqs
+
+
 register_position("rotary", RotaryPosition)
+register_position("pair_rotary", PairRotary)
 register_position("none", NoPosition)

@@ -61,3 +61,54 @@ class RoutedGLU(FeedForward):
 
 
 register_feed_forward("routed_glu", RoutedGLU)
+
+
+class RoutedExperts(FeedForward):
+    """Experts of two matrices, ``W_down act(W_up h)`` with ``act = relu^2``, stored as
+    ``<prefix>.e<i>.up|down``; no biases.  Router scores ``sigmoid(W_r h)`` (or the softmax over all
+    experts) in 32-bit, the ``top_k`` largest chosen (lowest index among equals), the scores as
+    weights, as they are or renormalised over the chosen ones.  ``weight_on="input"``: the weight
+    multiplies what the expert reads, ``sum_e expert_e(w_e h)``; the first grouped product scales
+    its accumulator by ``w_e`` before the activation, which is that product.  ``"output"``:
+    ``sum_e w_e expert_e(h)``."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int,
+                 score: str = "sigmoid", renormalize: bool = False, weight_on: str = "input",
+                 prefix: str = "mlp"):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.E, self.top = int(num_experts), int(top_k)
+        if not (0 < self.top <= self.E):
+            raise ValueError(f"{self.top} of {self.E} experts cannot be chosen")
+        if score not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
+            raise ValueError(f"score {score!r} / weight_on {weight_on!r} are not known")
+        self.score, self.renormalize, self.weight_on = score, bool(renormalize), weight_on
+        self.prefix = prefix + "." if prefix else ""
+
+    def tensor_specs(self):
+        h, f = self.hidden_size, self.intermediate_size
+        out = []
+        for e in range(self.E):
+            p = f"{self.prefix}e{e}."
+            out += [TensorSpec(p + "up", (f, h)), TensorSpec(p + "down", (h, f))]
+        out.append(TensorSpec(self.prefix + "router", (self.E, h)))
+        return out
+
+    def load(self, tensors, dtype, device):
+        p = self.prefix
+        self.w_up = torch.stack([tensors[f"{p}e{e}.up"] for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([tensors[f"{p}e{e}.down"] for e in range(self.E)]).contiguous()
+        self.router = ops.Linear(tensors[p + "router"], None, out_dtype=torch.float32)
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        idx, wgt = moe.route(self.router(x), self.top, self.renormalize, self.score)
+        plan = moe.Plan(idx, self.E, moe.on_tensor_cores(x.dtype, self.hidden_size,
+                                                         self.intermediate_size)
+                        and x.stride(0) % 8 == 0)
+        on_input = self.weight_on == "input"
+        y = moe.grouped_relu2(x, self.w_up, plan, wgt if on_input else None)
+        return moe.combine(moe.grouped_down(y, self.w_down, plan), plan,
+                           None if on_input else wgt, T)
+
+
+register_feed_forward("routed_experts", RoutedExperts)

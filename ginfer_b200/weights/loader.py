@@ -50,7 +50,7 @@ def kept_dtype(role: str, stored: torch.dtype, compute: torch.dtype) -> torch.dt
     """The dtype a tensor of ``role`` stored as ``stored`` has in memory."""
     if role == "int":
         return torch.int32
-    if role == "f32":
+    if role in ("f32", "norm32"):
         return torch.float32
     if compute == torch.float32:
         return torch.float32

@@ -35,7 +35,7 @@ def draw_tensor(spec, seed: int, std: float = 0.02, device="cpu") -> torch.Tenso
         return torch.randint(0, spec.int_high, spec.shape, generator=g, dtype=torch.int32,
                              device=device)
     t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * std
-    if spec.role == "norm":
+    if spec.role in ("norm", "norm32"):
         t += 1.0
     return t
 

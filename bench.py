@@ -260,7 +260,7 @@ def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
 
 
 # ----------------------------------------------------------------------------- another design
-# ``--design vilepel``: prefill and decode throughput of the Vilepel design at layer sizes that
+# ``--design vilepel|zolapel``: prefill and decode throughput of another design at layer sizes that
 # resemble a real model's (random weights), beside Qwen2 at equal width, heads, feed-forward size
 # and layer count.  The default workload and its JSON line are untouched by this option.
 def vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top, expert_ff,
@@ -284,6 +284,28 @@ def vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top,
             "layers": [dict(kinds[i % 4][0](), mlp=kinds[i % 4][1]) for i in range(layers)]}
 
 
+def zolapel_config(width, heads, kv_heads, dim, window, experts, top, expert_ff, side, layers,
+                   loop, vocab=32768):
+    """Layers of normed, gated attention and routed relu^2 experts with a token side input; the
+    layers ``loop[0] .. loop[1]-1`` run ``loop[2]`` times."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+             "mask": {"size": window},
+             "rot": {"base": 500000.0, "dims": dim,
+                     "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    return {"architecture": "Zolapel", "width": width, "vocab": vocab, "norm": {"eps": 1e-5},
+            "residual_mult": 0.5, "token_side": {"dim": side}, "torch_dtype": "bfloat16",
+            "loop": dict(zip(("start", "stop", "times"), loop)),
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(layers)]}
+
+
+ZOLAPEL_SIZES = {
+    # width, heads, kv heads, dim, window, experts, top, expert ff, side dim
+    "s": (1024, 8, 2, 64, 512, 16, 2, 1056, 64),
+    "m": (2048, 16, 4, 128, 1024, 32, 4, 2112, 128),
+}
+
+
 DESIGN_SIZES = {
     # width, heads, dim, rot, vdim, kv_rank, window, dense ff, experts, top, expert ff
     "s": (1024, 8, 64, 32, 64, 256, 512, 2816, 16, 2, 704),
@@ -291,23 +313,46 @@ DESIGN_SIZES = {
 }
 
 
+def design_configs(design: str, name: str, layers: int) -> dict:
+    """The design's configuration at size ``name`` and Qwen2 beside it at equal size."""
+    if design == "zolapel":
+        # two of the layers run twice; Qwen2 gets as many layers as Zolapel has runs, the same
+        # attention sizes and window, and a dense feed-forward of the three-matrix kind with the
+        # arithmetic of the `top` two-matrix experts a token uses (3 ff = 2 top expert_ff)
+        width, heads, kv, dim, window, experts, top, eff, side = ZOLAPEL_SIZES[name]
+        loop = (2, 4, 2) if layers >= 4 else (0, 1, 2)
+        runs = layers + (loop[1] - loop[0]) * (loop[2] - 1)
+        return {
+            "zolapel": zolapel_config(width, heads, kv, dim, window, experts, top, eff, side,
+                                      layers, loop),
+            "qwen2": dict(QWEN2_1P5B, num_hidden_layers=runs, hidden_size=width,
+                          num_attention_heads=heads, num_key_value_heads=kv, head_dim=dim,
+                          intermediate_size=2 * top * eff // 3, vocab_size=32768,
+                          use_sliding_window=True, sliding_window=window, max_window_layers=0),
+        }
+    width, heads, dim, rot, vdim, rank, window, ff, experts, top, eff = DESIGN_SIZES[name]
+    return {
+        "vilepel": vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top,
+                                  eff, layers),
+        "qwen2": dict(QWEN2_1P5B, num_hidden_layers=layers, hidden_size=width,
+                      num_attention_heads=heads, num_key_value_heads=max(1, heads // 4),
+                      head_dim=dim, intermediate_size=ff, vocab_size=32768,
+                      use_sliding_window=True, sliding_window=window, max_window_layers=0),
+    }
+
+
 def run_design(args) -> int:
     import torch
 
     from ginfer_b200.engine.llm import Engine
-    out = {"design": "vilepel", "beside": "qwen2 at equal width, heads, feed-forward and layers",
+    out = {"design": args.design,
+           "beside": "qwen2 at equal width, heads, feed-forward arithmetic and layer runs",
            "dtype": "bfloat16", "data": "synthetic", "sizes": {}}
     layers = args.layers or 8
-    for name in (args.size.split(",") if args.size else sorted(DESIGN_SIZES)):
-        width, heads, dim, rot, vdim, rank, window, ff, experts, top, eff = DESIGN_SIZES[name]
-        cfgs = {
-            "vilepel": vilepel_config(width, heads, dim, rot, vdim, rank, window, ff, experts, top,
-                                      eff, layers),
-            "qwen2": dict(QWEN2_1P5B, num_hidden_layers=layers, hidden_size=width,
-                          num_attention_heads=heads, num_key_value_heads=max(1, heads // 4),
-                          head_dim=dim, intermediate_size=ff, vocab_size=32768,
-                          use_sliding_window=True, sliding_window=window, max_window_layers=0),
-        }
+    sizes = ZOLAPEL_SIZES if args.design == "zolapel" else DESIGN_SIZES
+    for name in (args.size.split(",") if args.size else sorted(sizes)):
+        cfgs = design_configs(args.design, name, layers)
+        width = sizes[name][0]
         res = {}
         for which, cfg in cfgs.items():
             eng = Engine(config=cfg, weights_seed=0, dtype="bfloat16", max_num_batched_tokens=8192,
@@ -636,7 +681,7 @@ def main() -> int:
                     help="tokens a step of the long prompt in --scenario longctx (default 2,048)")
     ap.add_argument("--scenario", choices=SCENARIOS, default=None,
                     help="run a serving workload through the entry point instead of the benchmark")
-    ap.add_argument("--design", choices=["vilepel"], default=None,
+    ap.add_argument("--design", choices=["vilepel", "zolapel"], default=None,
                     help="measure another design beside Qwen2 at equal size instead of the benchmark")
     ap.add_argument("--size", default=None, help="with --design: sizes to run, e.g. s,m")
     args = ap.parse_args()

@@ -28,6 +28,12 @@
 // cluster of two CTAs on a tile of 256 tokens, every role as above in both CTAs except that only
 // the first CTA's warp 1 issues products (tcgen05.mma.cta_group::2, 256 x 256 x 16) and that its
 // barriers count both CTAs' loads and both CTAs' epilogue threads.
+// Grouped products (template parameter GROUPED; single CTAs): the rows of x are sorted by group
+// (the (token, expert) pairs of a routed feed-forward, sorted by expert), W holds one matrix a
+// group ([groups * N, K]), and a list in device memory names the row tiles: tile i starts at row
+// tile_row0[i] and belongs to group tile_expert[i], whose rows end at offsets[group + 1].  A tile
+// may reach into the next group's rows; those rows are computed and not stored.  The list's length
+// is read on the device, so nothing returns to the host between routing and the products.
 // Every wait is bounded; a wait that runs out sets *err (1 producer, 2 MMA issuer, 3 epilogue)
 // and the roles leave their loops, after which the CTA frees its tensor memory and returns.
 #include "tc_common.cuh"
@@ -106,6 +112,18 @@ __host__ __device__ constexpr uint32_t umma_idesc_pair(int bn) {
 constexpr int PEPI_STORE = 0;                 // out[m, n] = acc (+ bias[n])
 constexpr int PEPI_GATED = 2;                 // out[m, n / 2] = silu(acc[m, n]) * acc[m, n + 1], n even
 constexpr int PEPI_QKV = 3;                   // + bias, q and k heads rotated, k and v to the cache
+constexpr int PEPI_RELU2 = 4;                 // out[m, n] = relu(bf16(acc * w[m]))^2 (grouped only)
+
+// The row tiles of a grouped product (see the top of the file).  row_w (nullable) holds a weight
+// per (token, choice) pair and pair_of_pos the pair at each sorted row, for PEPI_RELU2.
+struct GroupArgs {
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* offsets;
+  const int* num_tiles;
+  const int* pair_of_pos;
+  const float* row_w;
+};
 // A warp's scratch: 32 rows of 64 bytes; the 16-byte pieces of a row are swapped by bits 1 and 2 of
 // the row, so that neither a thread a row nor four threads a row meet a bank twice in one access.
 constexpr int QKV_SCRATCH_WARP = 32 * 64;
@@ -148,12 +166,13 @@ __device__ __forceinline__ void store8_bf16(void* dst, const float (&v)[16], int
   *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(p);
 }
 
-template <int EPI, typename OUT, bool PAIR = false>
+template <int EPI, typename OUT, bool PAIR = false, bool GROUPED = false>
 __global__ void __launch_bounds__(P_THREADS)
 gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     const __grid_constant__ CUtensorMap tmap_w, const float* __restrict__ bias,
                     OUT* __restrict__ out, int ldo, int M, int N, int K, const QkvArgs qkv,
-                    int* __restrict__ err) {
+                    int* __restrict__ err, const GroupArgs grp = GroupArgs{}) {
+  static_assert(!(PAIR && GROUPED), "grouped products run on single CTAs");
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
   constexpr int NST = PAIR ? PSTAGES_PAIR : PSTAGES;
@@ -180,8 +199,8 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int walkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   constexpr int TM = PAIR ? 2 * PM : PM;
-  const int m_tiles = (M + TM - 1) / TM, n_tiles = (N + PN - 1) / PN;
-  const int ntiles = m_tiles * n_tiles;
+  int m_tiles = (M + TM - 1) / TM;
+  const int n_tiles = (N + PN - 1) / PN;
   const int nkb = (K + BK - 1) / BK;
 
   pdl_trigger();
@@ -217,6 +236,11 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (PAIR) cluster_sync();                    // the peer's barriers exist before anything signals them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  if (GROUPED) {
+    pdl_wait();                                // the list of row tiles comes from a kernel ahead
+    m_tiles = grp.num_tiles[0];
+  }
+  const int ntiles = m_tiles * n_tiles;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -224,8 +248,12 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
       int it = 0;                                      // K blocks issued so far, over all tiles
       bool ok = true;
       for (int tile = walker; tile < ntiles && ok; tile += walkers) {
-        const int n0 = (tile / m_tiles) * PN + (PAIR ? (int)rank * (PN / 2) : 0);
-        const int m0 = (tile % m_tiles) * TM + (int)rank * PM;
+        int n0 = (tile / m_tiles) * PN + (PAIR ? (int)rank * (PN / 2) : 0);
+        int m0 = (tile % m_tiles) * TM + (int)rank * PM;
+        if (GROUPED) {                                 // the group's matrix; the tile's first row
+          n0 += grp.tile_expert[tile % m_tiles] * N;
+          m0 = grp.tile_row0[tile % m_tiles];
+        }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % NST;
           if (!mbar_wait(empty + s, ((it / NST) & 1) ^ 1, err, 1)) { ok = false; break; }
@@ -308,9 +336,17 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
     for (int tile = walker; tile < ntiles; tile += walkers, ++t) {
       const int buf = t & 1, use = t >> 1;
       const int n0 = (tile / m_tiles) * PN + half * (PN / 2);
-      const int m = (tile % m_tiles) * TM + (int)rank * PM + q * 32 + lane;
+      int m = (tile % m_tiles) * TM + (int)rank * PM + q * 32 + lane;
+      float row_scale = 1.f;
+      if (GROUPED) {                                   // rows past the group's end are not stored
+        const int mt = tile % m_tiles, row0 = grp.tile_row0[mt];
+        const int end = grp.offsets[grp.tile_expert[mt] + 1];
+        m = row0 + q * 32 + lane;
+        if (m >= end) m = M;
+        if (EPI == PEPI_RELU2 && grp.row_w && m < M) row_scale = grp.row_w[grp.pair_of_pos[m]];
+      }
       const float* bias_t = bias_s + buf * PN + half * (PN / 2);     // of this thread's columns
-      if (EPI != PEPI_GATED && bias) {
+      if (EPI != PEPI_GATED && EPI != PEPI_RELU2 && bias) {
         const int tn0 = (tile / m_tiles) * PN;
         for (int i = e * 32 + lane; i < PN; i += EPI_WARPS * 32)
           bias_s[buf * PN + i] = tn0 + i < N ? bias[tn0 + i] : 0.f;
@@ -474,8 +510,15 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         const int n = n0 + c;
         if (m >= M || n >= N) continue;
-        if (EPI == PEPI_STORE) {
-          if (bias) {
+        if (EPI == PEPI_RELU2) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float u = fmaxf(round_bf16(v[j] * row_scale), 0.f);
+            v[j] = u * u;
+          }
+        }
+        if (EPI == PEPI_STORE || EPI == PEPI_RELU2) {
+          if (EPI == PEPI_STORE && bias) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] += bias_t[c + j];
           }
@@ -539,15 +582,15 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
   }
 }
 
-template <int EPI, typename OUT, bool PAIR = false>
+template <int EPI, typename OUT, bool PAIR = false, bool GROUPED = false>
 static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out,
                           int ldo, int M, int N, int K, int* err, int ctas, cudaStream_t st,
-                          const QkvArgs& qkv = QkvArgs{}) {
+                          const QkvArgs& qkv = QkvArgs{}, const GroupArgs& grp = GroupArgs{}) {
   constexpr int NST = PAIR ? PSTAGES_PAIR : PSTAGES;
   const size_t smem = 1024 + (size_t)NST * (PA_BYTES + (PAIR ? PB_BYTES_PAIR : PB_BYTES)) +
                       (2 * NST + 5) * sizeof(uint64_t) + 32 + 2 * PN * sizeof(float) +
                       (EPI == PEPI_QKV ? EPI_WARPS * QKV_SCRATCH_WARP : 0);
-  auto k = gemm_prefill_kernel<EPI, OUT, PAIR>;
+  auto k = gemm_prefill_kernel<EPI, OUT, PAIR, GROUPED>;
   static OncePerDevice attrs;                        // (of this instantiation of the launcher)
   if (int rc = attrs.run([&] {
         return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -555,9 +598,9 @@ static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const fl
     return rc;
   if (PAIR)
     return launch_kernel_cluster_dims(k, dim3(ctas & ~1), dim3(P_THREADS), smem, st, 2, true, mx, mw,
-                                      bias, (OUT*)out, ldo, M, N, K, qkv, err);
+                                      bias, (OUT*)out, ldo, M, N, K, qkv, err, grp);
   return launch_kernel(k, dim3(ctas), dim3(P_THREADS), smem, st, mx, mw, bias, (OUT*)out, ldo, M,
-                       N, K, qkv, err);
+                       N, K, qkv, err, grp);
 }
 
 }  // namespace gf
@@ -654,4 +697,51 @@ GF_EXPORT int gf_gemm_prefill_qkv(const void* x, int ldx, const void* w, const v
   const QkvArgs args{rope, positions, slot_mapping, (bf16*)kpages, (bf16*)vpages, nh, nkv, hd};
   return launch_prefill<PEPI_QKV, bf16>(mx, mw, (const float*)bias, out, ldo, M, N, K, err, ctas,
                                         (cudaStream_t)stream, args);
+}
+
+// Grouped products over rows sorted by group: a [P, K] bf16 (row stride lda), w [groups * N, K]
+// bf16 contiguous, row tiles of gf_gemm_grouped_tile_rows() rows listed on the device (tile_expert,
+// tile_row0, num_tiles[0] of them, at most max_tiles; offsets[g + 1] ends group g's rows).
+// epi 0: out [P, N] fp32 or bf16 = a w_g^T; epi 2: w rows interleaved (gate_i, up_i), act holds
+// {limit, alpha, shift} (or null for SiLU), out [P, N / 2] bf16; epi 4: out [P, N] bf16 =
+// relu(row_w[pair_of_pos[row]] * (a w_g^T))^2 (row_w null: 1).  -6: not served.
+GF_EXPORT int gf_gemm_grouped_tile_rows() { return PM; }
+
+GF_EXPORT int gf_gemm_grouped(const void* a, int lda, const void* w, int groups, int N, int K,
+                              const int* tile_expert, const int* tile_row0, const int* offsets,
+                              const int* num_tiles, int max_tiles, const int* pair_of_pos,
+                              const float* row_w, const float* act, void* out, int ldo, int P,
+                              int epi, int out_f32, int* err, void* stream) {
+  if (P <= 0 || N <= 0 || max_tiles <= 0) return 0;
+  if (K < 8 || K % 8 || lda % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) ||
+      ((uintptr_t)out & 15))
+    return -6;
+  if (epi == PEPI_GATED ? (N % 16 || ldo % 8 || out_f32)
+                        : ((epi != PEPI_STORE && epi != PEPI_RELU2) || N % 8 ||
+                           ldo % (out_f32 ? 4 : 8) || (epi == PEPI_RELU2 && out_f32)))
+    return -6;
+  if (epi == PEPI_RELU2 && row_w && !pair_of_pos) return -6;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, a, P, K, lda, PM)) return -6;
+  if ((long long)groups * N > 0x7fffffffLL) return -6;
+  if (!make_map(&mw, w, groups * N, K, K, PN)) return -6;
+  int sms = 148, dev = 0, v = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+    sms = v;
+  const long long most = (long long)max_tiles * ((N + PN - 1) / PN);
+  const int ctas = most < sms ? (int)most : sms;
+  const GroupArgs grp{tile_expert, tile_row0, offsets, num_tiles, pair_of_pos, row_w};
+  auto st = (cudaStream_t)stream;
+  if (epi == PEPI_GATED)
+    return launch_prefill<PEPI_GATED, bf16, false, true>(mx, mw, act, out, ldo, P, N, K, err, ctas,
+                                                         st, QkvArgs{}, grp);
+  if (epi == PEPI_RELU2)
+    return launch_prefill<PEPI_RELU2, bf16, false, true>(mx, mw, nullptr, out, ldo, P, N, K, err,
+                                                         ctas, st, QkvArgs{}, grp);
+  if (out_f32)
+    return launch_prefill<PEPI_STORE, float, false, true>(mx, mw, nullptr, out, ldo, P, N, K, err,
+                                                          ctas, st, QkvArgs{}, grp);
+  return launch_prefill<PEPI_STORE, bf16, false, true>(mx, mw, nullptr, out, ldo, P, N, K, err, ctas,
+                                                       st, QkvArgs{}, grp);
 }

@@ -363,6 +363,23 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
     }
 }
 
+// xs[s, :] = x[pair_of_pos[s] / top, :]: the tokens' rows in sorted order, 16 bytes an access, for
+// the grouped product that reads its rows by TMA (K % 8 == 0, 16-byte aligned rows).
+__global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+                                       const int* __restrict__ pair_of_pos, int top, int P, int K,
+                                       __nv_bfloat16* __restrict__ xs) {
+  pdl_trigger();
+  pdl_wait();
+  const int k8 = K >> 3;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)P * k8;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t s = i / k8;
+    const int c = (int)(i - s * k8) * 8;
+    const size_t src = (size_t)(pair_of_pos[s] / top) * ldx + c;
+    *reinterpret_cast<uint4*>(xs + s * K + c) = *reinterpret_cast<const uint4*>(x + src);
+  }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
                                    const float* __restrict__ wgt, int top, int N,
@@ -402,7 +419,7 @@ GF_EXPORT int gf_moe_plan(const int* idx, int P, int E, int tile_rows, int* offs
                           int* pos_of_pair, int* pair_of_pos, int* tile_expert, int* tile_row0,
                           int* num_tiles, void* stream) {
   if (P <= 0) return 0;
-  if (E > kMaxExperts || (tile_rows != kBM && tile_rows != kTM)) return -3;
+  if (E > kMaxExperts || tile_rows <= 0) return -3;
   return launch_kernel(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, idx, P, E,
                        tile_rows, offsets, pos_of_pair, pair_of_pos, tile_expert, tile_row0,
                        num_tiles);
@@ -443,6 +460,16 @@ GF_EXPORT int gf_moe_gemm(const void* a, int lda, const void* w, int N, int K, c
   if (first) GF_GO(bf, 1);
   GF_GO(bf, 0);
 #undef GF_GO
+}
+
+GF_EXPORT int gf_moe_gather_rows(const void* x, int ldx, const int* pair_of_pos, int top, int P,
+                                 int K, void* xs, void* stream) {
+  if (P <= 0) return 0;
+  if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)xs & 15)) return -3;
+  const size_t want = ((size_t)P * (K / 8) + 255) / 256;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  return launch_kernel(moe_gather_rows_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
+                       (const bf*)x, ldx, pair_of_pos, top, P, K, (bf*)xs);
 }
 
 GF_EXPORT int gf_moe_combine(const float* y, const int* pos_of_pair, const float* wgt, int T,

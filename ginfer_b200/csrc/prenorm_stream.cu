@@ -78,6 +78,131 @@ __global__ void stream_update_kernel(const float* __restrict__ x, const int* __r
   }
 }
 
+// Four channels of one type as one access.
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Quad<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+    uint2 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    h[0] = __floats2bfloat162_rn(v[0], v[1]);
+    h[1] = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+};
+
+// The same with four channels an access and the row kept in registers (OPT quads a thread): per
+// row this moves what the definition needs and nothing else.  Needs H % 4 == 0, H <= 4 * OPT *
+// threads and 16-byte aligned rows.
+template <typename Y, typename T, int OPT>
+__global__ void stream_update_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                         const Y* __restrict__ y, int ymode,
+                                         const float* __restrict__ scale, float m, float y_eps,
+                                         const float* __restrict__ add_full,
+                                         const float* __restrict__ add_row,
+                                         float* __restrict__ out, T* __restrict__ act, int norm,
+                                         const float* __restrict__ nw,
+                                         const float* __restrict__ nb, float norm_eps,
+                                         T* __restrict__ normed, int H) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x, nq = H >> 2;
+  pdl_trigger();
+  pdl_wait();
+  const size_t src = (size_t)(rows ? rows[r] : r) * H, dst = (size_t)r * H;
+  float v[OPT][4];
+  float yinv = 1.f;
+  if (ymode != 0) {
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < OPT; ++u) {
+      const int q = threadIdx.x + u * blockDim.x;
+      if (q < nq) {
+        Quad<Y>::load(y + src + 4 * q, v[u]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ss += v[u][i] * v[u][i];
+      }
+    }
+    if (ymode == 2) {
+      ss = block_sum(ss, scratch);
+      yinv = 1.f / sqrtf(ss / (float)H + y_eps);
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int u = 0; u < OPT; ++u) {
+    const int q = threadIdx.x + u * blockDim.x;
+    if (q < nq) {
+      float xv[4], t[4];
+      Quad<float>::load(x + src + 4 * q, xv);
+      if (add_full) {
+        Quad<float>::load(add_full + src + 4 * q, t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xv[i] += t[i];
+      }
+      if (add_row) {
+        Quad<float>::load(add_row + 4 * q, t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xv[i] += t[i];
+      }
+      if (ymode != 0) {
+        if (scale) Quad<float>::load(scale + 4 * q, t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (ymode == 1) xv[i] += m * (scale ? t[i] * v[u][i] : v[u][i]);
+          else xv[i] += m * (v[u][i] * yinv * t[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[u][i] = xv[i], sum += xv[i];
+      if (out) Quad<float>::store(out + dst + 4 * q, xv);
+      if (act) Quad<T>::store(act + dst + 4 * q, xv);
+    }
+  }
+  if (norm == 0) return;
+  float mean = 0.f;
+  if (norm == 1) mean = block_sum(sum, scratch) / (float)H;
+  float sq = 0.f;
+#pragma unroll
+  for (int u = 0; u < OPT; ++u) {
+    const int q = threadIdx.x + u * blockDim.x;
+    if (q < nq) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float d = v[u][i] - mean;
+        sq += d * d;
+      }
+    }
+  }
+  sq = block_sum(sq, scratch);
+  const float sd = sqrtf(sq / (float)H + norm_eps);
+#pragma unroll
+  for (int u = 0; u < OPT; ++u) {
+    const int q = threadIdx.x + u * blockDim.x;
+    if (q < nq) {
+      float w[4], b[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
+      Quad<float>::load(nw + 4 * q, w);
+      if (nb) Quad<float>::load(nb + 4 * q, b);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[i] = (v[u][i] - mean) / sd * w[i] + b[i];
+      Quad<T>::store(normed + dst + 4 * q, o);
+    }
+  }
+}
+
 // One warp per (token, head); heads 0 .. nh - 1 are q heads, nh .. nh + nkv - 1 the k heads.
 // qkv row: q heads from column 0, k heads from k_off, values from v_off (= k_off when the values
 // are the keys as projected).  freqs[n_pairs]; pair i of a head is channels (2i, 2i + 1) if
@@ -136,6 +261,96 @@ __global__ void qk_norm_rope_kernel(T* __restrict__ qkv, int stride, int num_tok
   }
 }
 
+// The same for neighbouring pairs and heads of up to 128 channels, a multiple of 4: a lane owns
+// four neighbouring channels (two pairs) and moves them as one access.
+template <typename T>
+__global__ void qk_norm_rope_vec_kernel(T* __restrict__ qkv, int stride, int num_tokens, int nh,
+                                        int nkv, int hd, int k_off, int v_off,
+                                        const float* __restrict__ qw, const float* __restrict__ kw,
+                                        float eps, const float* __restrict__ freqs, int n_pairs,
+                                        const int* __restrict__ positions,
+                                        const int* __restrict__ slot_mapping,
+                                        T* __restrict__ kpages, T* __restrict__ vpages) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();
+  const int heads = nh + nkv;
+  if (warp >= num_tokens * heads) return;
+  const int t = warp / heads, h = warp - t * heads;
+  const bool is_k = h >= nh;
+  if (is_k && slot_mapping == nullptr) return;
+  T* src = qkv + (size_t)t * stride + (is_k ? k_off + (h - nh) * hd : h * hd);
+  const float* w = is_k ? kw : qw;
+  const int c = 4 * lane;
+  const bool mine = c < hd;
+  T* dst = src;
+  float x[4] = {0.f, 0.f, 0.f, 0.f};
+  if (mine) Quad<T>::load(src + c, x);
+  if (is_k) {
+    const size_t slot = (size_t)slot_mapping[t];
+    dst = kpages + (slot * nkv + (h - nh)) * hd;
+    if (mine) {
+      T* vdst = vpages + (slot * nkv + (h - nh)) * hd + c;
+      if (v_off == k_off) {
+        Quad<T>::store(vdst, x);                     // exact: the values are the keys as projected
+      } else {
+        float vv[4];
+        Quad<T>::load(qkv + (size_t)t * stride + v_off + (h - nh) * hd + c, vv);
+        Quad<T>::store(vdst, vv);
+      }
+    }
+  }
+  float inv = 1.f;
+  if (w) {
+    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    ss = warp_sum(ss);
+    inv = 1.f / sqrtf(ss / (float)hd + eps);
+  }
+  if (!mine) return;
+  if (w) {
+    float wv[4];
+    Quad<float>::load(w + c, wv);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = x[i] * inv * wv[i];
+  }
+  const float pos = (float)positions[t];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int pair = 2 * lane + i;
+    if (pair < n_pairs) {
+      float sn, cs;
+      sincosf(pos * freqs[pair], &sn, &cs);
+      const float u = x[2 * i], v = x[2 * i + 1];
+      x[2 * i] = u * cs - v * sn;
+      x[2 * i + 1] = v * cs + u * sn;
+    }
+  }
+  Quad<T>::store(dst + c, x);
+}
+
+// Eight channels a thread (hd % 8 == 0, 16-byte aligned rows).
+__global__ void head_gate_vec_kernel(__nv_bfloat16* __restrict__ o,
+                                     const __nv_bfloat16* __restrict__ g, int g_stride, int nh,
+                                     int hd, size_t total8) {
+  pdl_trigger();
+  pdl_wait();
+  const int row8 = nh * hd / 8, hd8 = hd / 8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / row8;
+    const int h = (int)(i - t * row8) / hd8;
+    const float s = 1.f / (1.f + expf(-to_f32(g[t * g_stride + h])));
+    uint4 raw = *reinterpret_cast<const uint4*>(o + 8 * i);
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float2 a = __bfloat1622float2(p[u]);
+      p[u] = __floats2bfloat162_rn(a.x * s, a.y * s);
+    }
+    *reinterpret_cast<uint4*>(o + 8 * i) = raw;
+  }
+}
+
 template <typename T>
 __global__ void head_gate_kernel(T* __restrict__ o, const T* __restrict__ g, int g_stride, int nh,
                                  int hd, size_t total) {
@@ -191,6 +406,31 @@ GF_EXPORT int gf_stream_update(const float* x, const int* rows, const void* y, i
   if (R <= 0) return 0;
   if ((ymode != 0 && !y) || (ymode == 2 && !scale) || (norm != 0 && (!nw || !normed))) return -2;
   auto st = (cudaStream_t)stream;
+  const bool aligned = (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)add_full |
+                         (uintptr_t)add_row | (uintptr_t)out | (uintptr_t)act | (uintptr_t)nw |
+                         (uintptr_t)nb | (uintptr_t)normed) & 15) == 0;
+  if (H % 4 == 0 && H <= 4 * 4 * 256 && aligned) {
+    const int nq = H / 4;
+    const dim3 vgrid(R), vblock(nq <= 128 ? 128 : 256);
+#define GF_VEC(Y, T, OPT)                                                                         \
+  return launch_kernel(stream_update_vec_kernel<Y, T, OPT>, vgrid, vblock, 0, st, x, rows,          \
+                       (const Y*)y, ymode, scale, m, y_eps, add_full, add_row, out, (T*)act, norm,  \
+                       nw, nb, norm_eps, (T*)normed, H)
+#define GF_OPT(Y, T)                                  \
+  {                                                   \
+    if (nq <= (int)vblock.x) GF_VEC(Y, T, 1);         \
+    if (nq <= 2 * (int)vblock.x) GF_VEC(Y, T, 2);     \
+    GF_VEC(Y, T, 4);                                  \
+  }
+    if (act_dtype == GF_F32) {
+      if (y && y_dtype != GF_F32) return -2;
+      GF_OPT(float, float)
+    }
+    if (y && y_dtype == GF_F32) GF_OPT(float, bf)
+    GF_OPT(bf, bf)
+#undef GF_OPT
+#undef GF_VEC
+  }
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 48 * 1024) return -4;
   const dim3 grid(R), block(H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
@@ -217,6 +457,20 @@ GF_EXPORT int gf_qk_norm_rope(void* qkv, int stride, int T, int nh, int nkv, int
   auto st = (cudaStream_t)stream;
   const size_t warps = (size_t)T * (nh + nkv);
   const dim3 grid((unsigned)((warps + 3) / 4)), block(128);
+  const int esz = dtype == GF_F32 ? 4 : 2;
+  const bool vec = (interleaved || n_pairs == 0) && hd % 4 == 0 && hd <= 128 && stride % 4 == 0 &&
+                   k_off % 4 == 0 && v_off % 4 == 0 &&
+                   (((uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages) % (4 * esz)) == 0 &&
+                   (((uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
+  if (vec) {
+    if (dtype == GF_F32)
+      return launch_kernel(qk_norm_rope_vec_kernel<float>, grid, block, 0, st, (float*)qkv, stride,
+                           T, nh, nkv, hd, k_off, v_off, qw, kw, eps, freqs, n_pairs, positions,
+                           slot_mapping, (float*)kpages, (float*)vpages);
+    return launch_kernel(qk_norm_rope_vec_kernel<bf>, grid, block, 0, st, (bf*)qkv, stride, T, nh,
+                         nkv, hd, k_off, v_off, qw, kw, eps, freqs, n_pairs, positions,
+                         slot_mapping, (bf*)kpages, (bf*)vpages);
+  }
   if (dtype == GF_F32)
     return launch_kernel(qk_norm_rope_kernel<float>, grid, block, 0, st, (float*)qkv, stride, T,
                          nh, nkv, hd, k_off, v_off, qw, kw, eps, freqs, n_pairs, interleaved,
@@ -234,6 +488,9 @@ GF_EXPORT int gf_head_gate(void* o, const void* g, int g_stride, int T, int nh, 
   if (dtype == GF_F32)
     return launch_kernel(head_gate_kernel<float>, dim3(grid_for(total)), dim3(256), 0, st,
                          (float*)o, (const float*)g, g_stride, nh, hd, total);
+  if (hd % 8 == 0 && ((uintptr_t)o & 15) == 0)
+    return launch_kernel(head_gate_vec_kernel, dim3(grid_for(total / 8)), dim3(256), 0, st, (bf*)o,
+                         (const bf*)g, g_stride, nh, hd, total / 8);
   return launch_kernel(head_gate_kernel<bf>, dim3(grid_for(total)), dim3(256), 0, st, (bf*)o,
                        (const bf*)g, g_stride, nh, hd, total);
 }

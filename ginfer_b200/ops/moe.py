@@ -11,10 +11,32 @@ from . import _code, _cuda, _fn, _ok, _p, _stream, load_library
 _tile_rows: dict = {}
 
 
-def tile_rows(tensor_cores: bool) -> int:
+def tile_rows(tensor_cores) -> int:
+    """Rows of a tile of the plain kernel (``False``), of the ``mma.sync`` kernel (``True``) or of
+    the tcgen05 kernel (``"tcgen05"``)."""
     if tensor_cores not in _tile_rows:
-        _tile_rows[tensor_cores] = int(load_library("moe").gf_moe_tile_rows(int(tensor_cores)))
+        if tensor_cores == "tcgen05":
+            _tile_rows[tensor_cores] = int(load_library("gemm_prefill").gf_gemm_grouped_tile_rows())
+        else:
+            _tile_rows[tensor_cores] = int(load_library("moe").gf_moe_tile_rows(int(tensor_cores)))
     return _tile_rows[tensor_cores]
+
+
+# From this many (token, expert) pairs on, the grouped products of the bf16 path run on the
+# persistent tcgen05 kernel (csrc/gemm_prefill.cu, tiles of 128 rows x 256 columns, the rows brought
+# into sorted order first); below it on the mma.sync kernel with its tiles of 64 rows, which is
+# bound by the experts' weight bytes there.
+TCGEN05_MIN_PAIRS = 1024
+
+
+def kernel_for(x: torch.Tensor, pairs: int, reductions, widths) -> object:
+    """Which grouped-product kernel serves activations ``x`` with these reduction sizes and output
+    widths: ``"tcgen05"``, ``True`` (``mma.sync``) or ``False`` (plain)."""
+    if not (on_tensor_cores(x.dtype, *reductions) and x.stride(0) % 8 == 0):
+        return False
+    if pairs >= TCGEN05_MIN_PAIRS and all(n % 8 == 0 for n in widths):
+        return "tcgen05"
+    return True
 
 
 def on_tensor_cores(dtype: torch.dtype, *reductions: int) -> bool:
@@ -47,10 +69,11 @@ def route(logits: torch.Tensor, top: int, renormalize: bool, score: str = "softm
 class Plan:
     """Where every (token, choice) pair sits once the pairs are sorted by expert."""
 
-    def __init__(self, idx: torch.Tensor, num_experts: int, tensor_cores: bool = False):
+    def __init__(self, idx: torch.Tensor, num_experts: int, tensor_cores=False):
         T, top = idx.shape
+        self.tcgen05 = tensor_cores == "tcgen05"
         self.tensor_cores = bool(tensor_cores)
-        rows = tile_rows(self.tensor_cores)
+        rows = tile_rows("tcgen05" if self.tcgen05 else self.tensor_cores)
         P = T * top
         dev = idx.device
         self.pairs, self.top, self.num_experts = P, top, num_experts
@@ -75,16 +98,52 @@ class Plan:
 
 
 def grouped_glu(x: torch.Tensor, w_gate_up: torch.Tensor, plan: Plan, limit: float, alpha: float,
-                up_shift: float) -> torch.Tensor:
+                up_shift: float, act: torch.Tensor | None = None) -> torch.Tensor:
     """``x [T, K]``, ``w_gate_up [E, 2 F, K]`` (gate row, up row, ...) -> the activated gate/up
-    product of every pair, in sorted order: ``[P, F]``."""
+    product of every pair, in sorted order: ``[P, F]``.  ``act``: ``{limit, alpha, up_shift}`` as
+    an fp32 tensor on the device, for the tcgen05 kernel, which reads them from memory."""
     _cuda(x, w_gate_up)
     E, N, K = w_gate_up.shape
     assert x.dtype == w_gate_up.dtype and x.stride(1) == 1 and x.shape[1] == K
     assert w_gate_up.is_contiguous()
     out = torch.empty((plan.pairs, N // 2), dtype=x.dtype, device=x.device)
+    if plan.tcgen05:
+        if act is None:      # (a caller inside a CUDA graph brings the three constants on the device)
+            act = torch.tensor([limit, alpha, up_shift], dtype=torch.float32, device=x.device)
+        if _grouped_tc(gather_rows(x, plan), w_gate_up, plan, out, 2, act=act):
+            return out
+        raise RuntimeError("the tcgen05 grouped product refused a shape its plan was made for")
     _gemm(x, w_gate_up, plan, out, 1, limit, alpha, up_shift)
     return out
+
+
+def gather_rows(x: torch.Tensor, plan: Plan) -> torch.Tensor:
+    """The tokens' rows in the order of the sorted pairs, ``[P, K]``."""
+    K = x.shape[1]
+    xs = torch.empty((plan.pairs, K), dtype=x.dtype, device=x.device)
+    f = _fn("moe", "gf_moe_gather_rows", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                          c_void_p])
+    _ok(f(_p(x), x.stride(0), _p(plan.pair_of_pos), plan.top, plan.pairs, K, _p(xs), _stream()),
+        "moe_gather_rows")
+    return xs
+
+
+def _grouped_tc(a, w, plan: Plan, out, epi: int, act=None, row_w=None) -> bool:
+    """The grouped product on the persistent tcgen05 kernel; ``False`` if it refuses the shape."""
+    from .gemm_bf16 import _dev_state
+    E, N, K = w.shape
+    f = _fn("gemm_prefill", "gf_gemm_grouped",
+            [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p])
+    rc = f(_p(a), a.stride(0), _p(w), E, N, K, _p(plan.tile_expert), _p(plan.tile_row0),
+           _p(plan.offsets), _p(plan.num_tiles), plan.max_tiles, _p(plan.pair_of_pos), _p(row_w),
+           _p(act), _p(out), out.stride(0), plan.pairs, int(epi),
+           int(out.dtype == torch.float32), _p(_dev_state(a.device)["err"]), _stream())
+    if rc == -6:
+        return False
+    _ok(rc, "gemm_grouped")
+    return True
 
 
 def grouped_relu2(x: torch.Tensor, w_up: torch.Tensor, plan: Plan, row_weights=None
@@ -100,6 +159,10 @@ def grouped_relu2(x: torch.Tensor, w_up: torch.Tensor, plan: Plan, row_weights=N
         assert row_weights.dtype == torch.float32 and row_weights.is_contiguous()
         assert row_weights.numel() == plan.pairs
     out = torch.empty((plan.pairs, N), dtype=x.dtype, device=x.device)
+    if plan.tcgen05:
+        if _grouped_tc(gather_rows(x, plan), w_up, plan, out, 4, row_w=row_weights):
+            return out
+        raise RuntimeError("the tcgen05 grouped product refused a shape its plan was made for")
     _gemm(x, w_up, plan, out, 2, 0.0, 0.0, 0.0, row_weights)
     return out
 
@@ -110,6 +173,10 @@ def grouped_down(y: torch.Tensor, w_down: torch.Tensor, plan: Plan) -> torch.Ten
     E, N, K = w_down.shape
     assert y.dtype == w_down.dtype and y.is_contiguous() and y.shape == (plan.pairs, K)
     out = torch.empty((plan.pairs, N), dtype=torch.float32, device=y.device)
+    if plan.tcgen05:
+        if _grouped_tc(y, w_down, plan, out, 0):
+            return out
+        raise RuntimeError("the tcgen05 grouped product refused a shape its plan was made for")
     _gemm(y, w_down, plan, out, 0, 0.0, 0.0, 0.0)
     return out
 

@@ -49,14 +49,17 @@ class RoutedGLU(FeedForward):
         self.w_down = torch.stack([tensors[f"{self.prefix}e{e}.down"]
                                    for e in range(self.E)]).contiguous()    # [E, H, F]
         self.router = ops.Linear(tensors[self.prefix + "router"], None, out_dtype=torch.float32)
+        self.act = torch.tensor([self.limit, self.alpha, self.up_shift], dtype=torch.float32,
+                                device=device)
 
     def forward(self, x, ctx):
         T = x.shape[0]
         idx, wgt = moe.route(self.router(x), self.top, self.renormalize)
-        plan = moe.Plan(idx, self.E, moe.on_tensor_cores(x.dtype, self.hidden_size,
-                                                         self.intermediate_size)
-                        and x.stride(0) % 8 == 0)
-        y = moe.grouped_glu(x, self.w_gate_up, plan, self.limit, self.alpha, self.up_shift)
+        plan = moe.Plan(idx, self.E, moe.kernel_for(
+            x, T * self.top, (self.hidden_size, self.intermediate_size),
+            (self.intermediate_size, self.hidden_size)))
+        y = moe.grouped_glu(x, self.w_gate_up, plan, self.limit, self.alpha, self.up_shift,
+                            act=self.act)
         return moe.combine(moe.grouped_down(y, self.w_down, plan), plan, wgt, T)
 
 
@@ -102,9 +105,9 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         T = x.shape[0]
         idx, wgt = moe.route(self.router(x), self.top, self.renormalize, self.score)
-        plan = moe.Plan(idx, self.E, moe.on_tensor_cores(x.dtype, self.hidden_size,
-                                                         self.intermediate_size)
-                        and x.stride(0) % 8 == 0)
+        plan = moe.Plan(idx, self.E, moe.kernel_for(
+            x, T * self.top, (self.hidden_size, self.intermediate_size),
+            (self.intermediate_size, self.hidden_size)))
         on_input = self.weight_on == "input"
         y = moe.grouped_relu2(x, self.w_up, plan, wgt if on_input else None)
         return moe.combine(moe.grouped_down(y, self.w_down, plan), plan,

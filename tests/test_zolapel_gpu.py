@@ -193,6 +193,20 @@ def test_portions_of_the_large_kernels(tmp_path_factory, dtype):
     check(rows, expected(d, reqs, dtype), dtype, reqs)
 
 
+def test_a_long_portion_takes_the_tcgen05_grouped_products(tmp_path_factory):
+    """Six hundred tokens in one step are 1,200 and 1,800 (token, expert) pairs in the routed
+    layers: enough for the grouped products on tcgen05, whose results follow the plain model like
+    the others'."""
+    from ginfer_b200.ops import moe
+    cfg = tz.MIXED
+    d = folder(tmp_path_factory, "MIXED", cfg, "bfloat16")
+    reqs = prompts(cfg["vocab"], [600, 70], seed=12)
+    assert 600 * 2 >= moe.TCGEN05_MIN_PAIRS
+    steps = replay.cut_whole(reqs)
+    rows = replay.run_in_process(make_runner(d, "bfloat16", replay.peak_tokens(steps)), steps)
+    check(rows, expected(d, reqs, "bfloat16"), "bfloat16", reqs)
+
+
 # ----------------------------------------------------------------------------- a key that stands out
 def _needle_tokens(W, conf):
     """A (probe, needle) pair of tokens whose score towers over the probe's score with any other
@@ -479,3 +493,46 @@ def test_grouped_expert_products_scale_the_input(act, K, F):
             want1[t] += w * plain.expert(x[t:t + 1].double().numpy(), up[e].double().numpy(),
                                          down[e].double().numpy(), rnd)[0]
     assert np.allclose(out1.numpy(), want1, atol=tol * np.abs(want1).max(), rtol=tol)
+
+
+@pytest.mark.parametrize("K, F, T, E, top", [(256, 136, 1500, 6, 3), (64, 264, 700, 3, 2),
+                                             (2048, 512, 1024, 40, 4)])
+def test_grouped_products_on_tcgen05_equal_the_mma_kernel(K, F, T, E, top):
+    """Many pairs: the persistent tcgen05 kernel over rows brought into sorted order, tiles that
+    reach into the next expert's rows, experts with no rows, column tiles past an expert's matrix.
+    Both first products (scaled relu^2 and the clamped gated one) and the down product against the
+    ``mma.sync`` kernel on the same pairs; the scaled one also against plain arithmetic."""
+    from ginfer_b200.ops import gemm_bf16, moe
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(T, K, generator=g).bfloat16().cuda()
+    up = (torch.randn(E, F, K, generator=g) * K ** -0.5).bfloat16().cuda()
+    gate_up = (torch.randn(E, 2 * F, K, generator=g) * K ** -0.5).bfloat16().cuda()
+    down = (torch.randn(E, K, F, generator=g) * F ** -0.5).bfloat16().cuda()
+    idx = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).int()
+    idx[idx == 1] = 0 if E > 3 else 2                    # an expert without rows
+    idx[:, 1] = torch.where(idx[:, 1] == idx[:, 0], (idx[:, 0] + 1) % E, idx[:, 1])
+    wgt = (torch.rand(T, top, generator=g) + 0.2).cuda()
+    assert moe.kernel_for(x, T * top, (K, F), (F, K)) == "tcgen05"
+    tc, mma = moe.Plan(idx.cuda(), E, "tcgen05"), moe.Plan(idx.cuda(), E, True)
+    assert tc.tcgen05 and not mma.tcgen05
+
+    def by_pair(rows, plan):                             # sorted rows back in pair order
+        return rows[plan.pos_of_pair.long()].float()
+    y_tc, y_mma = moe.grouped_relu2(x, up, tc, wgt), moe.grouped_relu2(x, up, mma, wgt)
+    ref = by_pair(y_mma, mma)
+    assert torch.allclose(by_pair(y_tc, tc), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+    t = 7
+    for k, e in enumerate(idx[t].tolist()):
+        a = (x[t].double() @ up[e].double().T) * float(wgt[t, k])
+        want = torch.relu(a.bfloat16().double()) ** 2
+        got = y_tc[tc.pos_of_pair[t * top + k].long()].double()
+        assert torch.allclose(got, want, atol=2e-2 * float(want.abs().max()), rtol=2e-2)
+    z_tc = moe.grouped_glu(x, gate_up, tc, 1.25, 1.702, 1.0)
+    z_mma = moe.grouped_glu(x, gate_up, mma, 1.25, 1.702, 1.0)
+    ref = by_pair(z_mma, mma)
+    assert torch.allclose(by_pair(z_tc, tc), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+    d_tc = moe.combine(moe.grouped_down(y_tc, down, tc), tc, None, T)
+    d_mma = moe.combine(moe.grouped_down(y_tc[tc.pos_of_pair.long()][mma.pair_of_pos.long()]
+                                         .contiguous(), down, mma), mma, None, T)
+    assert torch.allclose(d_tc, d_mma, atol=1e-2 * float(d_mma.abs().max()), rtol=1e-2)
+    gemm_bf16.check_errors("cuda:0")

@@ -113,16 +113,25 @@ __global__ void moe_plan_kernel(const int* __restrict__ idx, int P, int E, int t
   for (int e = threadIdx.x >> 5; e < E; e += blockDim.x >> 5) {
     const int lane = threadIdx.x & 31;
     int at = start[e];
-    for (int p0 = 0; p0 < P; p0 += 32) {
-      const int p = p0 + lane;
-      const bool mine = p < P && idx[p] == e;
-      const unsigned m = __ballot_sync(0xffffffffu, mine);
-      if (mine) {
-        const int pos = at + __popc(m & ((1u << lane) - 1));
-        pos_of_pair[p] = pos;
-        pair_of_pos[pos] = p;
+    for (int p0 = 0; p0 < P; p0 += 32 * 8) {          // eight loads under way at a time
+      int got[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int p = p0 + 32 * u + lane;
+        got[u] = p < P ? idx[p] : -1;
       }
-      at += __popc(m);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int p = p0 + 32 * u + lane;
+        const bool mine = got[u] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+          const int pos = at + __popc(m & ((1u << lane) - 1));
+          pos_of_pair[p] = pos;
+          pair_of_pos[pos] = p;
+        }
+        at += __popc(m);
+      }
     }
   }
 }

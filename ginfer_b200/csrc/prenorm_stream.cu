@@ -5,7 +5,9 @@
 //                            y / rms(y) times a weight; x' leaves as the fp32 stream, as its
 //                            rounding to the activation type, and as norm(x') for the sublayer
 //                            that follows (layer norm with weight and bias, or RMS norm), each
-//                            only where asked for.  Row selection for the final norm.
+//                            only where asked for.  Row selection for the final norm.  y may
+//                            also be the rows of a routed feed-forward's (token, expert) pairs:
+//                            the kernel then adds up a token's pairs itself, in the order chosen.
 //   * qk_norm_rope_kernel    per (token, head): RMS norm over the head's channels with one weight
 //                            vector for all heads, rotation of channel pairs by position * f_i
 //                            (neighbouring pairs (2i, 2i+1) or halves (i, i + n)), q in place,
@@ -29,7 +31,9 @@ __global__ void stream_update_kernel(const float* __restrict__ x, const int* __r
                                      const float* __restrict__ add_row, float* __restrict__ out,
                                      T* __restrict__ act, int norm, const float* __restrict__ nw,
                                      const float* __restrict__ nb, float norm_eps,
-                                     T* __restrict__ normed, int H) {
+                                     T* __restrict__ normed, int H,
+                                     const int* __restrict__ pos_of_pair,
+                                     const float* __restrict__ pair_w, int top) {
   extern __shared__ float row[];
   __shared__ float scratch[33];
   const int r = blockIdx.x;
@@ -40,7 +44,16 @@ __global__ void stream_update_kernel(const float* __restrict__ x, const int* __r
   if (ymode != 0) {
     float ss = 0.f;
     for (int j = threadIdx.x; j < H; j += blockDim.x) {
-      const float v = to_f32(y[src + j]);
+      float v;
+      if (top > 0) {                         // y[pair rows]: the token's pairs added up in order
+        v = 0.f;
+        for (int k = 0; k < top; ++k) {
+          const size_t pr = (src / H) * top + k;
+          v = fmaf(pair_w ? pair_w[pr] : 1.f, to_f32(y[(size_t)pos_of_pair[pr] * H + j]), v);
+        }
+      } else {
+        v = to_f32(y[src + j]);
+      }
       row[j] = v;
       ss += v * v;
     }
@@ -117,7 +130,9 @@ __global__ void stream_update_vec_kernel(const float* __restrict__ x, const int*
                                          float* __restrict__ out, T* __restrict__ act, int norm,
                                          const float* __restrict__ nw,
                                          const float* __restrict__ nb, float norm_eps,
-                                         T* __restrict__ normed, int H) {
+                                         T* __restrict__ normed, int H,
+                                         const int* __restrict__ pos_of_pair,
+                                         const float* __restrict__ pair_w, int top) {
   __shared__ float scratch[33];
   const int r = blockIdx.x, nq = H >> 2;
   pdl_trigger();
@@ -131,7 +146,20 @@ __global__ void stream_update_vec_kernel(const float* __restrict__ x, const int*
     for (int u = 0; u < OPT; ++u) {
       const int q = threadIdx.x + u * blockDim.x;
       if (q < nq) {
-        Quad<Y>::load(y + src + 4 * q, v[u]);
+        if (top > 0) {                       // y[pair rows]: the token's pairs added up in order
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[u][i] = 0.f;
+          for (int k = 0; k < top; ++k) {
+            const size_t pr = (src / H) * top + k;
+            const float pw = pair_w ? pair_w[pr] : 1.f;
+            float t[4];
+            Quad<Y>::load(y + (size_t)pos_of_pair[pr] * H + 4 * q, t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[u][i] = fmaf(pw, t[i], v[u][i]);
+          }
+        } else {
+          Quad<Y>::load(y + src + 4 * q, v[u]);
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) ss += v[u][i] * v[u][i];
       }
@@ -261,8 +289,10 @@ __global__ void qk_norm_rope_kernel(T* __restrict__ qkv, int stride, int num_tok
   }
 }
 
-// The same for neighbouring pairs and heads of up to 128 channels, a multiple of 4: a lane owns
-// four neighbouring channels (two pairs) and moves them as one access.
+// The same for neighbouring pairs and heads of up to 128 channels, a multiple of 4: a block a
+// token, which takes the sines and cosines of the token's angles once, into shared memory, for all
+// of its heads; a warp a head at a time, a lane owns four neighbouring channels (two pairs) and
+// moves them as one access.
 template <typename T>
 __global__ void qk_norm_rope_vec_kernel(T* __restrict__ qkv, int stride, int num_tokens, int nh,
                                         int nkv, int hd, int k_off, int v_off,
@@ -271,14 +301,19 @@ __global__ void qk_norm_rope_vec_kernel(T* __restrict__ qkv, int stride, int num
                                         const int* __restrict__ positions,
                                         const int* __restrict__ slot_mapping,
                                         T* __restrict__ kpages, T* __restrict__ vpages) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  extern __shared__ float tab[];                     // cos[n_pairs], sin[n_pairs]
+  const int t = blockIdx.x, lane = threadIdx.x & 31;
   pdl_trigger();
   pdl_wait();
-  const int heads = nh + nkv;
-  if (warp >= num_tokens * heads) return;
-  const int t = warp / heads, h = warp - t * heads;
+  {
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x)
+      sincosf(pos * freqs[i], &tab[n_pairs + i], &tab[i]);
+  }
+  __syncthreads();
+  const int heads = slot_mapping ? nh + nkv : nh;    // nothing is cached: the k heads are left
+  for (int h = threadIdx.x >> 5; h < heads; h += blockDim.x >> 5) {
   const bool is_k = h >= nh;
-  if (is_k && slot_mapping == nullptr) return;
   T* src = qkv + (size_t)t * stride + (is_k ? k_off + (h - nh) * hd : h * hd);
   const float* w = is_k ? kw : qw;
   const int c = 4 * lane;
@@ -306,26 +341,25 @@ __global__ void qk_norm_rope_vec_kernel(T* __restrict__ qkv, int stride, int num
     ss = warp_sum(ss);
     inv = 1.f / sqrtf(ss / (float)hd + eps);
   }
-  if (!mine) return;
+  if (!mine) continue;
   if (w) {
     float wv[4];
     Quad<float>::load(w + c, wv);
 #pragma unroll
     for (int i = 0; i < 4; ++i) x[i] = x[i] * inv * wv[i];
   }
-  const float pos = (float)positions[t];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int pair = 2 * lane + i;
     if (pair < n_pairs) {
-      float sn, cs;
-      sincosf(pos * freqs[pair], &sn, &cs);
+      const float cs = tab[pair], sn = tab[n_pairs + pair];
       const float u = x[2 * i], v = x[2 * i + 1];
       x[2 * i] = u * cs - v * sn;
       x[2 * i + 1] = v * cs + u * sn;
     }
   }
   Quad<T>::store(dst + c, x);
+  }
 }
 
 // Eight channels a thread (hd % 8 == 0, 16-byte aligned rows).
@@ -402,8 +436,11 @@ GF_EXPORT int gf_stream_update(const float* x, const int* rows, const void* y, i
                                int ymode, const float* scale, float m, float y_eps,
                                const float* add_full, const float* add_row, float* out, void* act,
                                int act_dtype, int norm, const float* nw, const float* nb,
-                               float norm_eps, void* normed, int R, int H, void* stream) {
+                               float norm_eps, void* normed, int R, int H,
+                               const int* pos_of_pair, const float* pair_w, int top,
+                               void* stream) {
   if (R <= 0) return 0;
+  if (top > 0 && (!pos_of_pair || ymode == 0)) return -2;
   if ((ymode != 0 && !y) || (ymode == 2 && !scale) || (norm != 0 && (!nw || !normed))) return -2;
   auto st = (cudaStream_t)stream;
   const bool aligned = (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)add_full |
@@ -415,7 +452,7 @@ GF_EXPORT int gf_stream_update(const float* x, const int* rows, const void* y, i
 #define GF_VEC(Y, T, OPT)                                                                         \
   return launch_kernel(stream_update_vec_kernel<Y, T, OPT>, vgrid, vblock, 0, st, x, rows,          \
                        (const Y*)y, ymode, scale, m, y_eps, add_full, add_row, out, (T*)act, norm,  \
-                       nw, nb, norm_eps, (T*)normed, H)
+                       nw, nb, norm_eps, (T*)normed, H, pos_of_pair, pair_w, top)
 #define GF_OPT(Y, T)                                  \
   {                                                   \
     if (nq <= (int)vblock.x) GF_VEC(Y, T, 1);         \
@@ -437,7 +474,7 @@ GF_EXPORT int gf_stream_update(const float* x, const int* rows, const void* y, i
 #define GF_GO(Y, T)                                                                             \
   return launch_kernel(stream_update_kernel<Y, T>, grid, block, smem, st, x, rows, (const Y*)y, \
                        ymode, scale, m, y_eps, add_full, add_row, out, (T*)act, norm, nw, nb,   \
-                       norm_eps, (T*)normed, H)
+                       norm_eps, (T*)normed, H, pos_of_pair, pair_w, top)
   if (act_dtype == GF_F32) {
     if (y && y_dtype != GF_F32) return -2;
     GF_GO(float, float);
@@ -463,11 +500,13 @@ GF_EXPORT int gf_qk_norm_rope(void* qkv, int stride, int T, int nh, int nkv, int
                    (((uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages) % (4 * esz)) == 0 &&
                    (((uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
   if (vec) {
+    const dim3 grid(T);
+    const size_t smem = 2 * (size_t)n_pairs * sizeof(float);
     if (dtype == GF_F32)
-      return launch_kernel(qk_norm_rope_vec_kernel<float>, grid, block, 0, st, (float*)qkv, stride,
+      return launch_kernel(qk_norm_rope_vec_kernel<float>, grid, block, smem, st, (float*)qkv, stride,
                            T, nh, nkv, hd, k_off, v_off, qw, kw, eps, freqs, n_pairs, positions,
                            slot_mapping, (float*)kpages, (float*)vpages);
-    return launch_kernel(qk_norm_rope_vec_kernel<bf>, grid, block, 0, st, (bf*)qkv, stride, T, nh,
+    return launch_kernel(qk_norm_rope_vec_kernel<bf>, grid, block, smem, st, (bf*)qkv, stride, T, nh,
                          nkv, hd, k_off, v_off, qw, kw, eps, freqs, n_pairs, positions,
                          slot_mapping, (bf*)kpages, (bf*)vpages);
   }

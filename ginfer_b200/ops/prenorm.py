@@ -15,20 +15,29 @@ NORM_NONE, NORM_LAYER, NORM_RMS = 0, 1, 2
 def stream_update(x: torch.Tensor, act_dtype: torch.dtype, *, y=None, scale=None, mult: float = 1.0,
                   y_rms_eps: float | None = None, add_full=None, add_row=None, rows=None,
                   want_out: bool = True, want_act: bool = False, norm: int = NORM_NONE,
-                  norm_weight=None, norm_bias=None, norm_eps: float = 0.0):
+                  norm_weight=None, norm_bias=None, norm_eps: float = 0.0, pairs=None):
     """``x' = x (+ add_full) (+ add_row) + mult * f(y)`` on the fp32 stream ``x [R, H]``, with
     ``f(y) = y * scale`` (``scale`` fp32 ``[H]`` or ``None``) or, with ``y_rms_eps``,
     ``y / sqrt(mean(y^2) + y_rms_eps) * scale``.  ``rows`` (int32) selects rows of the inputs
     first.  Returns ``(x' fp32 or None, x' in act_dtype or None, norm(x') in act_dtype or None)``
     where the norm is a layer norm (``NORM_LAYER``: weight and optional bias) or an RMS norm
-    (``NORM_RMS``), all sums in 32-bit."""
+    (``NORM_RMS``), all sums in 32-bit.  ``pairs = (pos_of_pair [R * top] int32, weights [R, top]
+    fp32 or None, top)``: ``y`` holds a row per (token, choice) pair and a token's ``y`` is the
+    sum of its pairs' rows (times their weights), added up in the order chosen."""
     _cuda(x, y, scale, add_full, add_row, rows, norm_weight, norm_bias)
+    pos_of_pair, pair_w, top = pairs if pairs is not None else (None, None, 0)
+    _cuda(pos_of_pair, pair_w)
     assert x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous()
     H = x.shape[1]
     R = x.shape[0] if rows is None else rows.numel()
     for v in (scale, add_row, norm_weight, norm_bias):
         assert v is None or (v.dtype == torch.float32 and v.numel() == H and v.is_contiguous())
-    if y is not None:
+    if pairs is not None:
+        assert y is not None and rows is None and y.is_contiguous() and y.shape[1] == H
+        assert pos_of_pair.dtype == torch.int32 and pos_of_pair.numel() == R * top
+        assert pair_w is None or (pair_w.dtype == torch.float32 and pair_w.numel() == R * top
+                                  and pair_w.is_contiguous())
+    elif y is not None:
         assert y.shape == x.shape and y.is_contiguous()
     if add_full is not None:
         assert add_full.shape == x.shape and add_full.dtype == torch.float32 \
@@ -46,11 +55,12 @@ def stream_update(x: torch.Tensor, act_dtype: torch.dtype, *, y=None, scale=None
     f = _fn("prenorm_stream", "gf_stream_update",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_float, c_void_p,
              c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
-             c_int, c_int, c_void_p])
+             c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
     rc = f(_p(x), _p(rows), _p(y), _code(y.dtype) if y is not None else 0, ymode, _p(scale),
            float(mult), float(y_rms_eps or 0.0), _p(add_full), _p(add_row), _p(out),
            _p(act) if act is not out else None, _code(act_dtype), int(norm), _p(norm_weight),
-           _p(norm_bias), float(norm_eps), _p(normed), R, H, _stream())
+           _p(norm_bias), float(norm_eps), _p(normed), R, H, _p(pos_of_pair), _p(pair_w), int(top),
+           _stream())
     if rc == -4:
         raise ValueError(f"rows of {H} channels do not fit the stream kernel's shared memory")
     _ok(rc, "stream_update")

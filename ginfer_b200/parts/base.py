@@ -150,6 +150,20 @@ class LazyNorm:
                                out_dtype=self.dtype)[1]
 
 
+@dataclass
+class PairSum:
+    """The output of a routed feed-forward, not added up yet: ``rows [P, H]`` fp32 holds a row per
+    (token, choice) pair in sorted order, pair ``t * top + k`` sits at ``pos_of_pair[t * top + k]``
+    and a token's output is the sum of its pairs' rows times ``weights [T, top]`` (``None``: 1).
+    A kernel that adds the output to the stream can add the pairs up itself; anything else calls
+    :meth:`materialize`."""
+    rows: torch.Tensor
+    pos_of_pair: torch.Tensor
+    weights: torch.Tensor | None
+    top: int
+    materialize: Callable[[], torch.Tensor]
+
+
 # ----------------------------------------------------------------------------- part interfaces
 class Part:
     """Base of every part."""
@@ -222,6 +236,9 @@ class Mixer(Part):
 class FeedForward(Part):
     takes_lazy_norm = False
     adds_residual = False
+    # A feed-forward that sets this takes the keyword ``defer_sum`` and may then return a
+    # :class:`PairSum` instead of its output.
+    can_defer_sum = False
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError

@@ -200,14 +200,18 @@ class ScaledPreNormBlock(Block):
     def _add(self, x, y, scale, ctx, then, want_act=False):
         """``x + mult * scale * y`` -> ``(x', x' in the activation dtype or None, then(x'))``."""
         from ..ops import prenorm
+        from .base import PairSum
+        kw = {}
+        if isinstance(y, PairSum):                   # the kernel adds a token's pairs up itself
+            kw["pairs"] = (y.pos_of_pair, y.weights, y.top)
+            y = y.rows
         fused = then.fused() if then is not None else None
         if then is not None and fused is None:       # a norm the kernel cannot apply: on its own
             x, act, _ = prenorm.stream_update(x, ctx.dtype, y=y, scale=scale, mult=self.mult,
-                                              want_act=want_act)
+                                              want_act=want_act, **kw)
             return x, act, then.forward(x, None, want_sum=False, out_dtype=ctx.dtype)[1]
-        kw = {}
         if fused is not None:
-            kw = dict(norm=fused[0], norm_weight=fused[1], norm_bias=fused[2], norm_eps=fused[3])
+            kw.update(norm=fused[0], norm_weight=fused[1], norm_bias=fused[2], norm_eps=fused[3])
         return prenorm.stream_update(x, ctx.dtype, y=y, scale=scale, mult=self.mult,
                                      want_act=want_act, **kw)
 
@@ -226,7 +230,10 @@ class ScaledPreNormBlock(Block):
         n_next = None
         if self.feed_forward is not None:
             x, _, n2 = self._add(x, a, self.scales[0], ctx, self.feed_forward_norm)
-            f = self.feed_forward.forward(n2, ctx)
+            if self.feed_forward.can_defer_sum:
+                f = self.feed_forward.forward(n2, ctx, defer_sum=True)
+            else:
+                f = self.feed_forward.forward(n2, ctx)
             x, act, n_next = self._add(x, f, self.scales[1], ctx,
                                        then if self.after is None else None, act_for_after)
         else:

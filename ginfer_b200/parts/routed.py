@@ -16,7 +16,7 @@ import torch
 
 from .. import ops
 from ..ops import moe
-from .base import FeedForward, TensorSpec, register_feed_forward
+from .base import FeedForward, PairSum, TensorSpec, register_feed_forward
 
 
 class RoutedGLU(FeedForward):
@@ -102,7 +102,9 @@ class RoutedExperts(FeedForward):
         self.w_down = torch.stack([tensors[f"{p}e{e}.down"] for e in range(self.E)]).contiguous()
         self.router = ops.Linear(tensors[p + "router"], None, out_dtype=torch.float32)
 
-    def forward(self, x, ctx):
+    can_defer_sum = True
+
+    def forward(self, x, ctx, defer_sum: bool = False):
         T = x.shape[0]
         idx, wgt = moe.route(self.router(x), self.top, self.renormalize, self.score)
         plan = moe.Plan(idx, self.E, moe.kernel_for(
@@ -110,8 +112,11 @@ class RoutedExperts(FeedForward):
             (self.intermediate_size, self.hidden_size)))
         on_input = self.weight_on == "input"
         y = moe.grouped_relu2(x, self.w_up, plan, wgt if on_input else None)
-        return moe.combine(moe.grouped_down(y, self.w_down, plan), plan,
-                           None if on_input else wgt, T)
+        rows, w = moe.grouped_down(y, self.w_down, plan), None if on_input else wgt
+        if defer_sum:
+            return PairSum(rows, plan.pos_of_pair, w, self.top,
+                           lambda: moe.combine(rows, plan, w, T))
+        return moe.combine(rows, plan, w, T)
 
 
 register_feed_forward("routed_experts", RoutedExperts)

@@ -536,3 +536,23 @@ def test_grouped_products_on_tcgen05_equal_the_mma_kernel(K, F, T, E, top):
                                          .contiguous(), down, mma), mma, None, T)
     assert torch.allclose(d_tc, d_mma, atol=1e-2 * float(d_mma.abs().max()), rtol=1e-2)
     gemm_bf16.check_errors("cuda:0")
+
+
+def test_stream_update_adds_a_token_s_pairs_up():
+    from ginfer_b200.ops import prenorm
+    g = torch.Generator(device="cuda").manual_seed(4)
+    for H, top in ((88, 3), (50, 1), (1024, 4)):
+        R = 21
+        x = torch.randn(R, H, generator=g, device="cuda")
+        rows = torch.randn(R * top, H, generator=g, device="cuda")
+        pos = torch.randperm(R * top, generator=g, device="cuda").int()
+        w = torch.rand(R, top, generator=g, device="cuda")
+        s = torch.randn(H, generator=g, device="cuda")
+        for weights in (None, w):
+            y = rows[pos.long()].view(R, top, H).double()
+            if weights is not None:
+                y = y * weights.double()[:, :, None]
+            want = x.double() + 0.5 * s.double() * y.sum(1)
+            out, _, _ = prenorm.stream_update(x, torch.bfloat16, y=rows, scale=s, mult=0.5,
+                                              pairs=(pos, weights, top))
+            assert torch.allclose(out.double(), want, atol=1e-5, rtol=1e-5)

@@ -5,7 +5,7 @@
 //                       (or the sigmoid of each logit), the `top` largest chosen (lowest index
 //                       among equals), their scores kept as weights (optionally renormalised over
 //                       the chosen ones).
-//   moe_plan_kernel     one block: (token, choice) pairs counted per expert, the experts' ranges in
+//   moe_plan_kernel     a block an expert: (token, choice) pairs counted per expert, the experts' ranges in
 //                       the sorted order, each pair's place, and the list of row tiles (expert,
 //                       first row) that the grouped products walk over.
 //   moe_gemm_mma_kernel the grouped products of the bf16 path, on the tensor cores (see there).
@@ -80,59 +80,70 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
 
 // Pairs p = t * top + k.  offsets[E + 1]; pos_of_pair[P]; pair_of_pos[P]; tiles: tile_expert[],
 // tile_row0[] (first sorted row of the tile), num_tiles[0].
-__global__ void moe_plan_kernel(const int* __restrict__ idx, int P, int E, int tile_rows,
-                                int* __restrict__ offsets, int* __restrict__ pos_of_pair,
-                                int* __restrict__ pair_of_pos, int* __restrict__ tile_expert,
-                                int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
-  __shared__ int count[kMaxExperts], start[kMaxExperts + 1];
+// A block an expert (one SM could not keep up: 8,192 pairs took 29 us in one block).  Every block
+// counts all experts' pairs for itself, so that it knows where its expert's rows and tiles begin
+// without waiting for another block; then its warps take equal runs of the pairs, count their
+// expert's pairs in them, and place them behind the runs before: a pair's place is the number of
+// earlier pairs of the same expert, whatever the grid.
+constexpr int kPlanThreads = 256, kPlanWarps = kPlanThreads / 32;
+__global__ void __launch_bounds__(kPlanThreads)
+moe_plan_kernel(const int* __restrict__ idx, int P, int E, int tile_rows,
+                int* __restrict__ offsets, int* __restrict__ pos_of_pair,
+                int* __restrict__ pair_of_pos, int* __restrict__ tile_expert,
+                int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
+  __shared__ int count[kMaxExperts], run_count[kPlanWarps], base[2];
+  const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_trigger();
   pdl_wait();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) count[i] = 0;
   __syncthreads();
-  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&count[idx[p]], 1);
+  // this block's expert by ballots over the warps' runs; the others by shared atomics
+  const int run = (((P + kPlanWarps - 1) / kPlanWarps) + 31) & ~31;
+  const int p_lo = warp * run, p_hi = min(P, p_lo + run);
+  int mine_in_run = 0;
+  for (int p0 = p_lo; p0 < p_hi; p0 += 32) {
+    const int p = p0 + lane;
+    const int g = p < p_hi ? idx[p] : -1;
+    if (g >= 0 && g != e) atomicAdd(&count[g], 1);
+    mine_in_run += __popc(__ballot_sync(0xffffffffu, g == e));
+  }
+  if (lane == 0) run_count[warp] = mine_in_run;
   __syncthreads();
   if (threadIdx.x == 0) {
+    int n = 0;
+    for (int w = 0; w < kPlanWarps; ++w) n += run_count[w];
+    count[e] = n;
     int at = 0, nt = 0;
-    for (int e = 0; e < E; ++e) {
-      start[e] = at;
-      offsets[e] = at;
-      for (int r = 0; r < count[e]; r += tile_rows) {
-        tile_expert[nt] = e;
-        tile_row0[nt] = at + r;
-        ++nt;
-      }
-      at += count[e];
+    for (int i = 0; i < e; ++i) {
+      at += count[i];
+      nt += (count[i] + tile_rows - 1) / tile_rows;
     }
-    start[E] = at;
-    offsets[E] = at;
-    num_tiles[0] = nt;
+    base[0] = at;
+    base[1] = nt;
+    offsets[e] = at;
+    if (e == E - 1) {
+      offsets[E] = at + n;
+      num_tiles[0] = nt + (n + tile_rows - 1) / tile_rows;
+    }
   }
   __syncthreads();
-  // places inside an expert's range in pair order (a pair's place is the number of earlier pairs
-  // of the same expert): deterministic, and a warp handles 32 pairs at a time per expert
-  for (int e = threadIdx.x >> 5; e < E; e += blockDim.x >> 5) {
-    const int lane = threadIdx.x & 31;
-    int at = start[e];
-    for (int p0 = 0; p0 < P; p0 += 32 * 8) {          // eight loads under way at a time
-      int got[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int p = p0 + 32 * u + lane;
-        got[u] = p < P ? idx[p] : -1;
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int p = p0 + 32 * u + lane;
-        const bool mine = got[u] == e;
-        const unsigned m = __ballot_sync(0xffffffffu, mine);
-        if (mine) {
-          const int pos = at + __popc(m & ((1u << lane) - 1));
-          pos_of_pair[p] = pos;
-          pair_of_pos[pos] = p;
-        }
-        at += __popc(m);
-      }
+  const int start = base[0], n_mine = count[e];
+  for (int r = threadIdx.x * tile_rows; r < n_mine; r += blockDim.x * tile_rows) {
+    tile_expert[base[1] + r / tile_rows] = e;
+    tile_row0[base[1] + r / tile_rows] = start + r;
+  }
+  int at = start;
+  for (int w = 0; w < warp; ++w) at += run_count[w];
+  for (int p0 = p_lo; p0 < p_hi; p0 += 32) {
+    const int p = p0 + lane;
+    const bool mine = p < p_hi && idx[p] == e;
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (mine) {
+      const int pos = at + __popc(m & ((1u << lane) - 1));
+      pos_of_pair[p] = pos;
+      pair_of_pos[pos] = p;
     }
+    at += __popc(m);
   }
 }
 
@@ -429,7 +440,7 @@ GF_EXPORT int gf_moe_plan(const int* idx, int P, int E, int tile_rows, int* offs
                           int* num_tiles, void* stream) {
   if (P <= 0) return 0;
   if (E > kMaxExperts || tile_rows <= 0) return -3;
-  return launch_kernel(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, idx, P, E,
+  return launch_kernel(moe_plan_kernel, dim3(E), dim3(kPlanThreads), 0, (cudaStream_t)stream, idx, P, E,
                        tile_rows, offsets, pos_of_pair, pair_of_pos, tile_expert, tile_row0,
                        num_tiles);
 }

@@ -500,7 +500,9 @@ GF_EXPORT int gf_qk_norm_rope(void* qkv, int stride, int T, int nh, int nkv, int
                    (((uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages) % (4 * esz)) == 0 &&
                    (((uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
   if (vec) {
-    const dim3 grid(T);
+    // few tokens: a warp a head, so that no warp walks over several heads one after the other
+    const int hw = nh + nkv < 16 ? nh + nkv : 16;
+    const dim3 grid(T), block(T <= 256 ? 32 * hw : 128);
     const size_t smem = 2 * (size_t)n_pairs * sizeof(float);
     if (dtype == GF_F32)
       return launch_kernel(qk_norm_rope_vec_kernel<float>, grid, block, smem, st, (float*)qkv, stride,

@@ -314,6 +314,30 @@ def test_greedy_generation_through_the_entry_point(tmp_path_factory, pages):
         eng.runner.cache.check()
 
 
+def test_command_line(tmp_path_factory, tmp_path):
+    cfg = tz.OTHER
+    d = folder(tmp_path_factory, "OTHER", cfg, "float32")
+    reqs = prompts(cfg["vocab"], [6, 11], seed=10)
+    f = tmp_path / "prompts.txt"
+    f.write_text("\n".join(json.dumps(t) for t in reqs.values()) + "\n")
+    r = subprocess.run([sys.executable, os.path.join(replay.ROOT, "bin", "ginfer_generate"),
+                        "--model-path", d, "--dtype", "float32", "--prompt-ids", str(f),
+                        "--max-tokens", "5", "--ignore-eos", "--max-num-seqs", "2",
+                        "--max-seq-len", "64", "--num-kvcache-blocks", "8"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(x) for x in r.stdout.strip().splitlines()]
+    conf, W = tz.read_folder(d)
+    for toks, line in zip(reqs.values(), lines):
+        seq = list(toks)
+        assert len(line["output_ids"]) == 5
+        for t in line["output_ids"]:
+            logits = plain.forward(seq, W, conf)[-1]
+            if int(np.argmax(logits)) != t:
+                assert float(logits.max() - logits[t]) < 1e-3 * float(np.abs(logits).max())
+            seq.append(t)
+
+
 # ----------------------------------------------------------------------------- kernels alone
 def test_stream_update_kernel():
     from ginfer_b200.ops import prenorm

@@ -15,7 +15,7 @@ from typing import Any, Mapping
 from .model_config import ConfigError
 from .vilepel_config import _eos, _need, _plain, _positive_int
 
-MIXER_KEYS = {"attention": ("heads", "kv_heads", "dim", "vdim", "scale")}
+MIXER_KEYS = {"attention": ("heads", "kv_heads", "dim", "scale")}
 _TOP_KEYS = ("architecture", "width", "vocab", "norm", "residual_mult", "token_side", "loop",
              "layers", "eos_token_id", "torch_dtype")
 
@@ -101,12 +101,12 @@ class ZolapelConfig:
                                   "times >= 1)")
         for i, L in enumerate(self.layers):
             m = L.mixer
-            for k in ("heads", "kv_heads", "dim", "vdim"):
+            for k in ("heads", "kv_heads", "dim"):
                 _positive_int(m[k], f"layers[{i}].mixer.{k}")
             if m["heads"] % m["kv_heads"]:
                 raise ConfigError(f"config.json: layers[{i}] has {m['heads']} heads for "
                                   f"{m['kv_heads']} kv heads")
-            if m["vdim"] != m["dim"]:
+            if m.get("vdim", m["dim"]) != m["dim"]:
                 raise ConfigError(f"config.json: layers[{i}]: the values are the keys as "
                                   f"projected, so vdim ({m['vdim']}) must equal dim ({m['dim']})")
             if m.get("mask") is not None:            # no mask: every earlier token is seen

@@ -383,6 +383,115 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
     }
 }
 
+// ---- the same grouped products for a handful of pairs (decode steps of few requests) ------------
+// There the work is the experts' weight bytes, and a tile of 64 rows that walks its whole reduction
+// alone keeps too few of them under way (4 pairs: 45 us for 35 MB).  Here a tile is up to 8 rows of
+// one expert, kept in shared memory; a block takes 16, 32 or 64 weight rows of that expert (the
+// fewer pairs, the fewer rows, so that enough blocks keep loads under way), a warp two
+// neighbouring rows at a time (a gate and its up value in the gated form), streamed once with
+// 16-byte loads, each lane a strided share of the reduction, a warp sum at the end.  The order of
+// the sums depends on K alone, so a pair's result does not depend on the batch.
+constexpr int kFewRows = 8, kFewWarps = 8, kFewChunkMax = 64;
+
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float (&v)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x, v[2 * i + 1] = f.y;
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kFewWarps * 32)
+moe_gemv_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w,
+                int N, int K, const int* __restrict__ offsets, const int* __restrict__ pair_of_pos,
+                int top, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                const int* __restrict__ num_tiles, void* __restrict__ out_, float limit,
+                float alpha, float up_shift, const float* __restrict__ row_w, int chunk) {
+  extern __shared__ __align__(16) __nv_bfloat16 xrows[];           // [kFewRows][K]
+  pdl_trigger();
+  pdl_wait();
+  if ((int)blockIdx.x >= num_tiles[0]) return;
+  const int e = tile_expert[blockIdx.x], row0 = tile_row0[blockIdx.x];
+  const int rows = min(kFewRows, offsets[e + 1] - row0);
+  const int k8 = K >> 3;
+  for (int i = threadIdx.x; i < rows * k8; i += blockDim.x) {
+    const int r = i / k8, c = (i - r * k8) * 8;
+    const int src = MODE != 0 ? pair_of_pos[row0 + r] / top : row0 + r;
+    *reinterpret_cast<uint4*>(xrows + (size_t)r * K + c) =
+        *reinterpret_cast<const uint4*>(a + (size_t)src * lda + c);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* we = w + (size_t)e * N * K;
+  for (int i = warp; i < chunk / 2; i += kFewWarps) {
+    const int n = blockIdx.y * chunk + 2 * i;
+    if (n >= N) break;                                             // N is even
+    const __nv_bfloat16 *w0 = we + (size_t)n * K, *w1 = w0 + K;
+    float acc0[kFewRows], acc1[kFewRows];
+#pragma unroll
+    for (int r = 0; r < kFewRows; ++r) acc0[r] = acc1[r] = 0.f;
+    // four steps of the reduction at a time: their eight loads go out together, before any
+    // arithmetic (left to the compiler, the loads of a step waited behind the branches of the
+    // step before: 1.2 TB/s)
+    for (int c0 = lane * 8; c0 < K; c0 += 4 * 256) {
+      uint4 wa[4], wb[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 256;
+        if (c < K) {
+          wa[u] = __ldg(reinterpret_cast<const uint4*>(w0 + c));
+          wb[u] = __ldg(reinterpret_cast<const uint4*>(w1 + c));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 256;
+        if (c >= K) break;
+        float f0[8], f1[8];
+        bf16x8_to_f32(wa[u], f0);
+        bf16x8_to_f32(wb[u], f1);
+#pragma unroll
+        for (int r = 0; r < kFewRows; ++r) {
+          if (r < rows) {
+            float x[8];
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(xrows + (size_t)r * K + c), x);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              acc0[r] = fmaf(f0[j], x[j], acc0[r]);
+              acc1[r] = fmaf(f1[j], x[j], acc1[r]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kFewRows; ++r) {
+      if (r >= rows) break;                                        // uniform over the warp
+      const float c0 = warp_sum(acc0[r]), c1 = warp_sum(acc1[r]);
+      if (lane != 0) continue;
+      const size_t s = (size_t)(row0 + r);
+      if (MODE == 2) {
+        const float rw = row_w ? row_w[pair_of_pos[s]] : 1.f;
+        const float u0 = fmaxf(to_f32(from_f32<__nv_bfloat16>(c0 * rw)), 0.f);
+        const float u1 = fmaxf(to_f32(from_f32<__nv_bfloat16>(c1 * rw)), 0.f);
+        __nv_bfloat16* out = (__nv_bfloat16*)out_ + s * N + n;
+        out[0] = from_f32<__nv_bfloat16>(u0 * u0);
+        out[1] = from_f32<__nv_bfloat16>(u1 * u1);
+      } else if (MODE == 1) {
+        const float gt = to_f32(from_f32<__nv_bfloat16>(c0)), up = to_f32(from_f32<__nv_bfloat16>(c1));
+        ((__nv_bfloat16*)out_)[s * (N / 2) + n / 2] =
+            from_f32<__nv_bfloat16>(clamped_glu(gt, up, limit, alpha, up_shift));
+      } else {
+        float* out = (float*)out_ + s * N + n;
+        out[0] = c0;
+        out[1] = c1;
+      }
+    }
+  }
+}
+
 // xs[s, :] = x[pair_of_pos[s] / top, :]: the tokens' rows in sorted order, 16 bytes an access, for
 // the grouped product that reads its rows by TMA (K % 8 == 0, 16-byte aligned rows).
 __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
@@ -424,7 +533,9 @@ using bf = __nv_bfloat16;
 GF_DEFINE_PDL_SWITCH
 
 // Rows of a tile: of the plain kernel (tensor_cores == 0) or of the tensor-core kernel.
-GF_EXPORT int gf_moe_tile_rows(int tensor_cores) { return tensor_cores ? kTM : kBM; }
+GF_EXPORT int gf_moe_tile_rows(int tensor_cores) {
+  return tensor_cores == 2 ? kFewRows : tensor_cores ? kTM : kBM;
+}
 
 // sigmoid != 0: a score is the sigmoid of its logit instead of the softmax over all experts.
 GF_EXPORT int gf_moe_route(const float* logits, int T, int E, int top, int renorm, int sigmoid,
@@ -451,9 +562,37 @@ GF_EXPORT int gf_moe_gemm(const void* a, int lda, const void* w, int N, int K, c
                           const int* pair_of_pos, int top, const int* tile_expert,
                           const int* tile_row0, const int* num_tiles, int max_tiles, void* out,
                           int first, float limit, float alpha, float up_shift,
-                          const float* row_w, int dtype, int tensor_cores, void* stream) {
+                          const float* row_w, int dtype, int tensor_cores, void* stream,
+                          int pairs) {
   if (max_tiles <= 0) return 0;
   auto st = (cudaStream_t)stream;
+  if (tensor_cores == 2) {                     // a handful of pairs: the weight-streaming kernel
+    const size_t smem = (size_t)kFewRows * K * sizeof(bf);
+    if (dtype != GF_BF16 || K % 8 || lda % 8 || N % 2 || (uintptr_t)a % 16 || (uintptr_t)w % 16 ||
+        smem > 64 * 1024)
+      return -3;
+    // at most min(pairs, max_tiles) tiles hold rows; about four blocks an SM should be busy
+    int chunk = kFewChunkMax;
+    const int busy = pairs > 0 && pairs < max_tiles ? pairs : max_tiles;
+    while (chunk > 2 * kFewWarps && (long long)busy * ((N + chunk - 1) / chunk) < 4 * 148) chunk /= 2;
+    const dim3 fgrid(max_tiles, (N + chunk - 1) / chunk), fblock(kFewWarps * 32);
+#define GF_FEW(MODE)                                                                              \
+  {                                                                                               \
+    static OncePerDevice attrs;                                                                   \
+    if (int rc = attrs.run([&] {                                                                  \
+          return cudaFuncSetAttribute(moe_gemv_kernel<MODE>,                                      \
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);    \
+        }))                                                                                       \
+      return rc;                                                                                  \
+    return launch_kernel(moe_gemv_kernel<MODE>, fgrid, fblock, smem, st, (const bf*)a, lda,        \
+                         (const bf*)w, N, K, offsets, pair_of_pos, top, tile_expert, tile_row0,    \
+                         num_tiles, out, limit, alpha, up_shift, row_w, chunk);                    \
+  }
+    if (first == 2) GF_FEW(2)
+    if (first) GF_FEW(1)
+    GF_FEW(0)
+#undef GF_FEW
+  }
   if (tensor_cores) {
     if (dtype != GF_BF16 || K % 8 || lda % 8 || (uintptr_t)a % 16 || (uintptr_t)w % 16) return -3;
     const dim3 tgrid(max_tiles, (N + kTN - 1) / kTN), tblock(256);

@@ -12,11 +12,13 @@ _tile_rows: dict = {}
 
 
 def tile_rows(tensor_cores) -> int:
-    """Rows of a tile of the plain kernel (``False``), of the ``mma.sync`` kernel (``True``) or of
-    the tcgen05 kernel (``"tcgen05"``)."""
+    """Rows of a tile of the plain kernel (``False``), of the ``mma.sync`` kernel (``True``), of
+    the tcgen05 kernel (``"tcgen05"``) or of the kernel for a handful of pairs (``"few"``)."""
     if tensor_cores not in _tile_rows:
         if tensor_cores == "tcgen05":
             _tile_rows[tensor_cores] = int(load_library("gemm_prefill").gf_gemm_grouped_tile_rows())
+        elif tensor_cores == "few":
+            _tile_rows[tensor_cores] = int(load_library("moe").gf_moe_tile_rows(2))
         else:
             _tile_rows[tensor_cores] = int(load_library("moe").gf_moe_tile_rows(int(tensor_cores)))
     return _tile_rows[tensor_cores]
@@ -27,15 +29,23 @@ def tile_rows(tensor_cores) -> int:
 # into sorted order first); below it on the mma.sync kernel with its tiles of 64 rows, which is
 # bound by the experts' weight bytes there.
 TCGEN05_MIN_PAIRS = 1024
+# Up to this many pairs (decode steps of few requests) the products run on the kernel that streams
+# an expert's rows once for up to eight pairs; it keeps the rows in shared memory, which bounds the
+# reduction size.
+FEW_MAX_PAIRS = 16
+FEW_MAX_K = 4096
 
 
 def kernel_for(x: torch.Tensor, pairs: int, reductions, widths) -> object:
     """Which grouped-product kernel serves activations ``x`` with these reduction sizes and output
-    widths: ``"tcgen05"``, ``True`` (``mma.sync``) or ``False`` (plain)."""
+    widths: ``"tcgen05"``, ``"few"`` (a handful of pairs), ``True`` (``mma.sync``) or ``False``
+    (plain)."""
     if not (on_tensor_cores(x.dtype, *reductions) and x.stride(0) % 8 == 0):
         return False
     if pairs >= TCGEN05_MIN_PAIRS and all(n % 8 == 0 for n in widths):
         return "tcgen05"
+    if pairs <= FEW_MAX_PAIRS and max(reductions) <= FEW_MAX_K and all(n % 2 == 0 for n in widths):
+        return "few"
     return True
 
 
@@ -72,12 +82,14 @@ class Plan:
     def __init__(self, idx: torch.Tensor, num_experts: int, tensor_cores=False):
         T, top = idx.shape
         self.tcgen05 = tensor_cores == "tcgen05"
+        self.few = tensor_cores == "few"
         self.tensor_cores = bool(tensor_cores)
-        rows = tile_rows("tcgen05" if self.tcgen05 else self.tensor_cores)
+        rows = tile_rows(tensor_cores if isinstance(tensor_cores, str) else self.tensor_cores)
         P = T * top
         dev = idx.device
         self.pairs, self.top, self.num_experts = P, top, num_experts
-        self.max_tiles = -(-P // rows) + num_experts
+        # every tile holds at least one pair, and every expert's last tile may be partly empty
+        self.max_tiles = min(-(-P // rows) + num_experts, P)
         ints = torch.empty(num_experts + 1 + 2 * P + 2 * self.max_tiles + 1, dtype=torch.int32,
                            device=dev)
         at = 0
@@ -185,11 +197,12 @@ def _gemm(a, w, plan, out, first, limit, alpha, up_shift, row_w=None):
     f = _fn("moe", "gf_moe_gemm",
             [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
              c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float, c_void_p,
-             c_int, c_int, c_void_p])
+             c_int, c_int, c_void_p, c_int])
     _ok(f(_p(a), a.stride(0), _p(w), w.shape[1], w.shape[2], _p(plan.offsets),
           _p(plan.pair_of_pos), plan.top, _p(plan.tile_expert), _p(plan.tile_row0),
           _p(plan.num_tiles), plan.max_tiles, _p(out), int(first), float(limit), float(alpha),
-          float(up_shift), _p(row_w), _code(a.dtype), int(plan.tensor_cores), _stream()),
+          float(up_shift), _p(row_w), _code(a.dtype), 2 if plan.few else int(plan.tensor_cores),
+          _stream(), plan.pairs),
         "moe_gemm")
 
 

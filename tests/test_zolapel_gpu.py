@@ -580,3 +580,39 @@ def test_stream_update_adds_a_token_s_pairs_up():
             out, _, _ = prenorm.stream_update(x, torch.bfloat16, y=rows, scale=s, mult=0.5,
                                               pairs=(pos, weights, top))
             assert torch.allclose(out.double(), want, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("K, F, T, E, top", [(256, 136, 1, 6, 3), (64, 264, 8, 3, 2),
+                                             (2048, 96, 16, 40, 4), (72, 88, 30, 5, 2)])
+def test_grouped_products_of_a_handful_of_pairs(K, F, T, E, top):
+    """Decode steps of few requests: the kernel that streams an expert's rows once for up to eight
+    pairs, against the ``mma.sync`` kernel on the same pairs (all three products); an expert with
+    more than eight pairs has several tiles."""
+    from ginfer_b200.ops import moe
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(T, K, generator=g).bfloat16().cuda()
+    up = (torch.randn(E, F, K, generator=g) * K ** -0.5).bfloat16().cuda()
+    gate_up = (torch.randn(E, 2 * F, K, generator=g) * K ** -0.5).bfloat16().cuda()
+    down = (torch.randn(E, K, F, generator=g) * F ** -0.5).bfloat16().cuda()
+    idx = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).int()
+    if T >= 16:
+        idx[:12, 0] = 2                                  # twelve pairs of one expert: two tiles
+        idx[:12, 1] = 0
+    wgt = (torch.rand(T, top, generator=g) + 0.2).cuda()
+    assert moe.kernel_for(x, T * top, (K, F), (F, K)) == ("few" if T * top <= moe.FEW_MAX_PAIRS
+                                                          else True)
+    few, mma = moe.Plan(idx.cuda(), E, "few"), moe.Plan(idx.cuda(), E, True)
+    assert few.few and not mma.few
+
+    def by_pair(rows, plan):
+        return rows[plan.pos_of_pair.long()].float()
+    for a, b in ((moe.grouped_relu2(x, up, few, wgt), moe.grouped_relu2(x, up, mma, wgt)),
+                 (moe.grouped_glu(x, gate_up, few, 1.25, 1.702, 1.0),
+                  moe.grouped_glu(x, gate_up, mma, 1.25, 1.702, 1.0))):
+        ref = by_pair(b, mma)
+        assert torch.allclose(by_pair(a, few), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+    y = moe.grouped_relu2(x, up, mma, wgt)
+    y_few = y[mma.pos_of_pair.long()][few.pair_of_pos.long()].contiguous()
+    d_few = moe.combine(moe.grouped_down(y_few, down, few), few, None, T)
+    d_mma = moe.combine(moe.grouped_down(y, down, mma), mma, None, T)
+    assert torch.allclose(d_few, d_mma, atol=1e-3 * float(d_mma.abs().max()), rtol=1e-3)

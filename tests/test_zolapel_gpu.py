@@ -207,6 +207,34 @@ def test_a_long_portion_takes_the_tcgen05_grouped_products(tmp_path_factory):
     check(rows, expected(d, reqs, "bfloat16"), "bfloat16", reqs)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_portion_shapes_replay_from_graphs(tmp_path_factory, dtype):
+    """Steps with a portion of 600 tokens (1,200 and 1,800 expert pairs: the tcgen05 grouped
+    products in bfloat16) come three times with the same shape, on other requests: from the
+    second time on such a step is captured and replayed from a CUDA graph (routing, the plan of
+    the pairs and the loop's entries included), and the logits are those of the eager engine."""
+    cfg = tz.MIXED
+    d = folder(tmp_path_factory, "MIXED", cfg, dtype)
+    reqs = prompts(cfg["vocab"], [640, 640, 640, 640], seed=14)
+    steps = []
+    for rid, toks in reqs.items():
+        steps.append({"step": len(steps), "end": [], "entries": [
+            {"id": rid, "tokens": toks[:600], "want": [0, 599]}]})
+        steps.append({"step": len(steps), "end": [rid], "entries": [
+            {"id": rid, "tokens": toks[600:], "want": [39]}]})
+    eager = replay.run_in_process(make_runner(d, dtype, 704), steps)
+    runner = make_runner(d, dtype, 704, eager=False)
+    graphs = replay.run_in_process(runner, steps)
+    assert any(isinstance(k[0], str) for k in runner._graphs), "no portion graph was captured"
+    assert runner.graph_launches > 0
+    for key, row in eager.items():
+        scale = float(np.abs(row).max())
+        assert float(np.abs(graphs[key] - row).max()) <= (1e-5 if dtype == "float32" else 2e-2) * scale, key
+    want = expected(d, reqs, dtype)
+    worst, where, _, _ = row_errors(graphs, want)
+    assert worst <= LIMIT[dtype][0], (where, worst)
+
+
 # ----------------------------------------------------------------------------- a key that stands out
 def _needle_tokens(W, conf):
     """A (probe, needle) pair of tokens whose score towers over the probe's score with any other

@@ -81,7 +81,8 @@ def row_errors(rows, want):
 # the format's rounding, and a row whose router scores or gates were close may differ more (at
 # most one row in thirty may be off for that); a misplaced page, a window off by one or a lost
 # pass of the loop puts most rows near one.
-LIMIT = {"float32": (2e-4, 5e-5), "bfloat16": (0.2, 0.05)}
+LIMIT = {"float32": (2e-4, 5e-5), "bfloat16": (0.2, 0.03)}
+P90 = {"float32": 1e-4, "bfloat16": 0.06}      # nine rows in ten are this close
 
 
 def check(rows, want, dtype, requests):
@@ -93,6 +94,7 @@ def check(rows, want, dtype, requests):
     else:
         assert worst <= LIMIT[dtype][0], f"worst row {where}: relative error {worst:.3e}"
     assert mean <= LIMIT[dtype][1], f"mean relative error {mean:.3e}"
+    assert sorted(errs)[int(0.9 * (len(errs) - 1))] <= P90[dtype], "one row in ten is off"
 
 
 # ----------------------------------------------------------------------------- mechanisms alone
@@ -644,3 +646,4 @@ def test_grouped_products_of_a_handful_of_pairs(K, F, T, E, top):
     d_few = moe.combine(moe.grouped_down(y_few, down, few), few, None, T)
     d_mma = moe.combine(moe.grouped_down(y, down, mma), mma, None, T)
     assert torch.allclose(d_few, d_mma, atol=1e-3 * float(d_mma.abs().max()), rtol=1e-3)
+

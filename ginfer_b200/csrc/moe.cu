@@ -551,8 +551,8 @@ GF_EXPORT int gf_moe_plan(const int* idx, int P, int E, int tile_rows, int* offs
                           int* num_tiles, void* stream) {
   if (P <= 0) return 0;
   if (E > kMaxExperts || tile_rows <= 0) return -3;
-  return launch_kernel(moe_plan_kernel, dim3(E), dim3(kPlanThreads), 0, (cudaStream_t)stream, idx, P, E,
-                       tile_rows, offsets, pos_of_pair, pair_of_pos, tile_expert, tile_row0,
+  return launch_kernel(moe_plan_kernel, dim3(E), dim3(kPlanThreads), 0, (cudaStream_t)stream, idx,
+                       P, E, tile_rows, offsets, pos_of_pair, pair_of_pos, tile_expert, tile_row0,
                        num_tiles);
 }
 

@@ -142,7 +142,7 @@ def cuts(reqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["MIXED", "OTHER"])
+@pytest.mark.parametrize("name", ["MIXED", "OTHER", "ODD"])
 def test_cuts_agree_with_plain(tmp_path_factory, name, dtype):
     cfg = getattr(tz, name)
     d = folder(tmp_path_factory, name, cfg, dtype)

@@ -71,6 +71,17 @@ OTHER = config([
           moe(experts=9, top=2, ff=20)),
 ], width=52, vocab=173, eps=1e-6, mult=1.0, side=0, loop=(0, 2, 3))
 
+# sizes that fit no vector access and no tensor-core tile: a head of 50 channels of which 6
+# rotate, experts of 36, a width of 100, a side input of 7; a window of one token (a token sees
+# itself only) and a window of two; the loop is the first layer alone
+ODD = config([
+    layer(attention(heads=3, kv_heads=1, dim=50, window=2, rot_dims=6, base=30.0, scale=0.5),
+          moe(experts=5, top=3, ff=36)),
+    layer(attention(heads=2, kv_heads=2, dim=18, window=1, rot_dims=18, scale=0.8), None),
+    layer(attention(heads=4, kv_heads=1, dim=32, window=None, rot_dims=None, scale=0.3),
+          moe(experts=2, top=1, ff=16)),
+], width=100, vocab=131, eps=1e-4, mult=0.8, side=7, loop=(0, 1, 2))
+
 ATTENTION_ONLY = config([layer(attention(window=19), None)], width=40, vocab=97, side=0)
 ROUTED = config([layer(attention(window=1000), moe(experts=7, top=3))], width=40, vocab=97, side=0)
 SIDE = config([layer(attention(window=1000), None), layer(attention(window=1000), None)],
